@@ -22,6 +22,9 @@ class KVSpec:
     # keys and values are the same rows (a latent that serves as both): the
     # store then keeps one tensor and hands it out as keys and as values
     shared_kv: bool = False
+    # with a window: the first so many positions of a sequence stay visible to every
+    # later query, so the pages that hold them are never given back
+    keep_first: int = 0
 
     @property
     def value_dim(self) -> int:

@@ -106,6 +106,16 @@ class KVGroup:
         self.pool.give(int(row[i]) for i in range(end_pages, have))
         self.end[slot] = end_pages
 
+    def _kept_pages(self) -> int:
+        """Pages at a sequence's start that a window never lets go of."""
+        return (self.spec.keep_first + PAGE_TOKENS - 1) // PAGE_TOKENS if self.spec.window else 0
+
+    def held_pages(self, slot: int):
+        """Indices into the slot's table row of the pages it holds: the kept first
+        pages, then everything from `first` on."""
+        first, end = self.first[slot], self.end[slot]
+        return list(range(0, min(self._kept_pages(), first, end))) + list(range(first, end))
+
     def trim(self, slot: int, length: int) -> None:
         """Give back pages that no query at a position >= `length` can see."""
         w = self.spec.window
@@ -113,7 +123,7 @@ class KVGroup:
             return
         first_visible = max(0, length - w + 1)
         keep_from = min(first_visible // PAGE_TOKENS, self.end[slot])
-        have = self.first[slot]
+        have = max(self.first[slot], min(self._kept_pages(), self.end[slot]))  # the kept first pages stay
         if keep_from > have:
             row = self.table_host[slot]
             self.pool.give(int(row[i]) for i in range(have, keep_from))
@@ -121,7 +131,7 @@ class KVGroup:
 
     def close(self, slot: int) -> None:
         row = self.table_host[slot]
-        self.pool.give(int(row[i]) for i in range(self.first[slot], self.end[slot]))
+        self.pool.give(int(row[i]) for i in self.held_pages(slot))
         del self.first[slot], self.end[slot]
         self._dirty.pop(slot, None)
 

@@ -36,7 +36,7 @@ class NormSpec:
 class PositionSpec:
     """A position encoding applied to query and key head vectors."""
 
-    kind: str  # "rope_neox"
+    kind: str  # "rope_neox"; "rope_scaled" (params: factor, low, high, original)
     head_dim: int
     rotary_dim: int
     theta: float
@@ -63,7 +63,9 @@ class MixerSpec:
     # what only some kinds have, by name: "latent_attention" reads q_rank, kv_rank,
     # eps and sink; "mlstm" reads gate_cap and eps; "conv_attention" reads kv taps,
     # temp_coef, temp_every, sink and distance_slopes; "rglru" reads width, blocks,
-    # taps and decay_scale; "pair" reads left and right (two `MixerSpec`s) and eps
+    # taps and decay_scale; "pair" reads left and right (two `MixerSpec`s) and eps;
+    # "gqa_attention" reads values_are_keys, output_gate and keep_first; "selective_scan"
+    # reads inner, state, dt_rank and taps
     params: Tuple[Tuple[str, Any], ...] = ()
     # size of a head's value vector when it differs from `head_dim`; 0: the same
     v_head_dim: int = 0
@@ -78,7 +80,7 @@ class MixerSpec:
 
 @dataclass(frozen=True)
 class FeedForwardSpec:
-    kind: str  # "swiglu"; "glu_clamped" (params: alpha, limit); "moe" (params: experts, top, activation,
+    kind: str  # "swiglu"; "relu2"; "glu_clamped" (params: alpha, limit); "moe" (params: experts, top, activation,
     # router_bias, scores, weight_input, alpha, limit, shared_ff, shared_limit)
     hidden_size: int
     intermediate_size: int
@@ -170,6 +172,10 @@ class ModelSpec:
     # the matrix of the runs that start from a mix of the stream and the embedding
     # output (`RunEntry.mixes_input`); None: the model has none
     stream_mix_name: Optional[str] = None
+    # the residual as this many parallel copies of the width (hyper-connections): the
+    # embedding output goes into every copy, the layers' blocks read and rewrite all of
+    # them ([rows, streams * hidden] 32-bit), and their sum meets the final norm
+    residual_streams: int = 1
 
     def __post_init__(self) -> None:
         if not self.run_order:

@@ -85,7 +85,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                         const __nv_bfloat16* __restrict__ v_pages, PagedKV cache,
                         const int* __restrict__ row_pos, const int* __restrict__ row_slot,
                         __nv_bfloat16* __restrict__ out, float* __restrict__ partial, int nq,
-                        int n_htiles, int n_splits, int window, float scale_log2,
+                        int n_htiles, int n_splits, int window, int keep_first, float scale_log2,
                         const float* __restrict__ sink, const float* __restrict__ slopes,
                         int cluster_merge, int trace_id, int* __restrict__ err) {
     constexpr int LD = D + 8;
@@ -130,10 +130,16 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     const int pos = row_pos[r], slot = row_slot[r];
     const int lo = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
     const int first_page = lo / PAGE, last_page = pos / PAGE;
-    const int n_pg = last_page - first_page + 1;
+    // The first `keep_first` positions stay visible beyond the window.  The pages walked
+    // are those that hold such positions and lie before the window's first page, then
+    // the window's pages: a list indexed by pg below, page `logical(pg)` of the sequence.
+    const int kept = min(keep_first, lo);
+    const int kp = min((kept + PAGE - 1) / PAGE, first_page);
+    auto logical = [&](int v) { return v < kp ? v : v - kp + first_page; };
+    const int n_pg = kp + last_page - first_page + 1;
     const int pps = (n_pg + n_splits - 1) / n_splits;
-    const int pg0 = first_page + split * pps;
-    const int pg1 = min(last_page + 1, pg0 + pps);
+    const int pg0 = split * pps;
+    const int pg1 = min(n_pg, pg0 + pps);
 
     const int* table = cache.page_table + (size_t)slot * cache.max_pages;
     auto issue = [&](int pg, int page, int buf) {
@@ -182,7 +188,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     // the loop.
     int pages_first[DEC_STAGES];
 #pragma unroll
-    for (int i = 0; i < DEC_STAGES; ++i) pages_first[i] = pg0 + i < pg1 ? table[pg0 + i] : 0;
+    for (int i = 0; i < DEC_STAGES; ++i) pages_first[i] = pg0 + i < pg1 ? table[logical(pg0 + i)] : 0;
     // Pages before the one that holds this row's own position were written by
     // earlier steps: their loads start before the wait on the preceding kernel,
     // which writes only the new key, value and query.  Positions, slots and the
@@ -190,8 +196,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     int issued = 0;
 #pragma unroll
     for (int i = 0; i < DEC_STAGES - 1; ++i) {
-        if (issued == i && pg0 + i < pg1 && pg0 + i < last_page) {
-            issue(pg0 + i, pages_first[i], i);
+        if (issued == i && pg0 + i < pg1 && logical(pg0 + i) < last_page) {
+            issue(logical(pg0 + i), pages_first[i], i);
             ++issued;
         }
     }
@@ -230,19 +236,19 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                 // own position), then the rest as their buffers come free
 #pragma unroll
                 for (int i = 0; i < DEC_STAGES - 1; ++i)
-                    if (i >= issued && pg0 + i < pg1) issue(pg0 + i, pages_first[i], i);
+                    if (i >= issued && pg0 + i < pg1) issue(logical(pg0 + i), pages_first[i], i);
                 int pg = pg0 + DEC_STAGES - 1;
-                int page_next = pg < pg1 ? table[pg] : 0;
+                int page_next = pg < pg1 ? table[logical(pg)] : 0;
                 for (; pg < pg1; ++pg) {
                     const int i = pg - pg0, buf = i % DEC_STAGES;
                     const int page = page_next;
-                    if (pg + 1 < pg1) page_next = table[pg + 1];
+                    if (pg + 1 < pg1) page_next = table[logical(pg + 1)];
                     // the four warps are done with what the buffer held: the page before
                     // this one in it, or, in the last buffer, the dry pass first
                     const int uses = i / DEC_STAGES + (buf == DEC_STAGES - 1 ? 1 : 0);  // of the buffer so far
                     if (uses > 0 && !sm100::mbar_wait(&empty_bar[buf], (uint32_t)((uses - 1) & 1)) && err)
                         atomicExch(err, 32);
-                    issue(pg, page, buf);
+                    issue(logical(pg), page, buf);
                 }
             }
             __syncwarp();
@@ -266,7 +272,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                 if (!sm100::mbar_wait(&full_bar[buf], (uint32_t)((i / DEC_STAGES) & 1)) && err) atomicExch(err, 31);
                 // The whole page came, rows past the sequence's end too, which nothing ever
                 // wrote: zero those value rows, since 0 * NaN is not 0 (their keys are masked)
-                const int valid = pos + 1 - pg * PAGE;
+                const int base = logical(pg) * PAGE;
+                const int valid = pos + 1 - base;
                 if (valid < PAGE) {
                     __nv_bfloat16* vt = vbuf + buf * TILE;
                     for (int e = tid; e < (PAGE - valid) * (D / 8); e += DEC_THREADS) {
@@ -278,8 +285,9 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                 }
                 const long long c2 = tracing ? clock64() : 0;
                 if (tracing) waited += c2 - c0;
-                const int base = pg * PAGE;
-                auto visible = [&](int key) { return base + key >= lo && base + key <= pos; };
+                auto visible = [&](int key) {
+                    return (base + key >= lo || base + key < keep_first) && base + key <= pos;
+                };
                 attend_keys16<D, true, PEN>(qf, kbuf + buf * TILE, vbuf + buf * TILE, warp * 16, scale_log2, visible,
                                        pen, pos - base, m, l, acc);
                 __syncwarp();
@@ -301,15 +309,18 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                 if (tracing) waited += c1 - c0;
                 const int nxt = pg + DEC_STAGES - 1;
                 const int page_now = page_ahead;
-                if (nxt + 1 < pg1) page_ahead = table[nxt + 1];
-                if (nxt < pg1) issue(nxt, page_now, (nxt - pg0) % DEC_STAGES);
+                if (nxt + 1 < pg1) page_ahead = table[logical(nxt + 1)];
+                if (nxt < pg1) issue(logical(nxt), page_now, (nxt - pg0) % DEC_STAGES);
                 else cp_async_commit();
                 if (tracing) issuing += clock64() - c1;
             }
             const long long c2 = tracing ? clock64() : 0;
-            const int base = pg * PAGE;
+            const int base = dry ? 0 : logical(pg) * PAGE;
             const int lo_eff = dry ? 0x7fffffff : lo;
-            auto visible = [&](int key) { return base + key >= lo_eff && base + key <= pos; };
+            const int keep_eff = dry ? 0 : keep_first;  // the dry pass sees no key
+            auto visible = [&](int key) {
+                return (base + key >= lo_eff || base + key < keep_eff) && base + key <= pos;
+            };
             attend_keys16<D, false, PEN>(qf, kbuf + buf * TILE, vbuf + buf * TILE, warp * 16, scale_log2, visible,
                                     pen, pos - base, m, l, acc);
             if (tracing && !dry) attending += clock64() - c2;
@@ -323,7 +334,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
 #pragma unroll
                 for (int i = 0; i < DEC_STAGES - 1; ++i) {
                     if (i >= issued) {
-                        if (pg0 + i < pg1) issue(pg0 + i, pages_first[i], i);
+                        if (pg0 + i < pg1) issue(logical(pg0 + i), pages_first[i], i);
                         else cp_async_commit();
                     }
                 }
@@ -532,7 +543,7 @@ const CUtensorMap* store_map(const void* base, long long rows, int D) {
 template <int D, bool TMA, bool PEN>
 int launch_decode(const void* q, const void* k_pages, const void* v_pages, long long pool_pages,
                   const PagedKV& cache, const int* row_pos, const int* row_slot, void* out, float* partial,
-                  int R, int nq, int n_splits, int window, float scale, const float* sink,
+                  int R, int nq, int n_splits, int window, int keep_first, float scale, const float* sink,
                   const float* slopes, int cluster_merge, int* err, cudaStream_t s) {
     constexpr int LD = D + 8;
     const int g = nq / cache.n_kv_heads;
@@ -585,7 +596,7 @@ int launch_decode(const void* q, const void* k_pages, const void* v_pages, long 
                     cluster_merge ? n_splits : 1, *mk, *mv,
                     (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages,
                     cache, row_pos, row_slot, (__nv_bfloat16*)out, partial, nq, n_htiles, n_splits, window,
-                    scale * LOG2E, sink, slopes, cluster_merge, g_dtrace_next++, err);
+                    keep_first, scale * LOG2E, sink, slopes, cluster_merge, g_dtrace_next++, err);
     if (e != cudaSuccess) return (int)e;
     if (n_splits > 1 && !cluster_merge)
         RFX_LAUNCH(attention_combine_kernel, R * nq, D <= 128 ? 64 : 128, 0, s, (const float*)partial,
@@ -596,7 +607,7 @@ int launch_decode(const void* q, const void* k_pages, const void* v_pages, long 
 int decode_entry(const void* q, const void* k_pages, const void* v_pages, const int* page_table,
                  int max_pages, int page_size, const int* row_pos, const int* row_slot, void* out,
                  float* partial, int R, int nq, int nkv, int head_dim, int n_splits, int window,
-                 float scale, const float* sink, const float* slopes, int cluster_merge,
+                 int keep_first, float scale, const float* sink, const float* slopes, int cluster_merge,
                  long long pool_pages, int* err, void* stream) {
     if (R <= 0) return 0;
     if (page_size != PAGE || nkv <= 0 || nq % nkv != 0 || n_splits < 1) return RFX_ERR_BAD_ARG;
@@ -618,9 +629,9 @@ int decode_entry(const void* q, const void* k_pages, const void* v_pages, const 
     // with slopes: the kernel's form that takes the distance term off the scores
 #define RFX_GO(DD, T)                                                                                              \
     (slopes ? launch_decode<DD, T, true>(q, k_pages, v_pages, pool_pages, cache, row_pos, row_slot, out, partial, \
-                                         R, nq, n_splits, window, scale, sink, slopes, cluster_merge, err, s)     \
+                                         R, nq, n_splits, window, keep_first, scale, sink, slopes, cluster_merge, err, s)     \
             : launch_decode<DD, T, false>(q, k_pages, v_pages, pool_pages, cache, row_pos, row_slot, out, partial, \
-                                          R, nq, n_splits, window, scale, sink, slopes, cluster_merge, err, s))
+                                          R, nq, n_splits, window, keep_first, scale, sink, slopes, cluster_merge, err, s))
 #define RFX_CASE(DD)                                        \
     case DD:                                                \
         if (DD % 64 == 0 && tma) {                          \
@@ -657,8 +668,23 @@ extern "C" int rfx_attention_decode(const void* q, const void* k_pages, const vo
                                     int n_splits, int window, float scale, const float* sink,
                                     const float* slopes, long long pool_pages, int* err, void* stream) {
     return decode_entry(q, k_pages, v_pages, page_table, max_pages, page_size, row_pos, row_slot, out,
-                        partial, R, nq, nkv, head_dim, n_splits, window, scale, sink, slopes, 0, pool_pages,
+                        partial, R, nq, nkv, head_dim, n_splits, window, 0, scale, sink, slopes, 0, pool_pages,
                         err, stream);
+}
+
+// The same with `keep_first`: the first so many positions of a sequence stay
+// visible beyond the window.
+extern "C" int rfx_attention_decode_kf(const void* q, const void* k_pages, const void* v_pages,
+                                       const int* page_table, int max_pages, int page_size,
+                                       const int* row_pos, const int* row_slot, void* out,
+                                       float* partial, int R, int nq, int nkv, int head_dim,
+                                       int n_splits, int window, int keep_first, float scale, const float* sink,
+                                       const float* slopes, long long pool_pages, int cluster, int* err,
+                                       void* stream) {
+    if (keep_first < 0) return RFX_ERR_BAD_ARG;
+    return decode_entry(q, k_pages, v_pages, page_table, max_pages, page_size, row_pos, row_slot, out,
+                        cluster ? nullptr : partial, R, nq, nkv, head_dim, n_splits, window, keep_first, scale,
+                        sink, slopes, cluster ? 1 : 0, pool_pages, err, stream);
 }
 
 // The same with 2, 4, 8 or (where the device places such a cluster) 16 splits that
@@ -675,7 +701,7 @@ extern "C" int rfx_attention_decode_cluster(const void* q, const void* k_pages, 
                                             float scale, const float* sink, const float* slopes,
                                             long long pool_pages, int* err, void* stream) {
     return decode_entry(q, k_pages, v_pages, page_table, max_pages, page_size, row_pos, row_slot, out,
-                        nullptr, R, nq, nkv, head_dim, n_splits, window, scale, sink, slopes, 1, pool_pages,
+                        nullptr, R, nq, nkv, head_dim, n_splits, window, 0, scale, sink, slopes, 1, pool_pages,
                         err, stream);
 }
 

@@ -6,7 +6,8 @@
 // code runs however the tokens are cut into steps or batched.
 //
 // For a query at position p of head h (kv head h / group): keys j in
-// [max(0, p - window + 1), p];  s_j = (q . K_j) * scale;  online softmax
+// [max(0, p - window + 1), p], and with `keep_first` also the keys j < keep_first
+// however far back they lie;  s_j = (q . K_j) * scale;  online softmax
 // m' = max(m, s), l = l e^(m-m') + e^(s-m'), acc = acc e^(m-m') + e^(s-m') V_j;
 // With `slopes` (one per query head) s_j loses slope * (p - j), a linear
 // distance bias.  out = acc / l   (src/kernels_cuda/attention_online.cuh:64-102; the window
@@ -32,7 +33,7 @@ __global__ void __launch_bounds__(128)
 attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,
                        const T* __restrict__ v_pages, PagedKV cache,
                        const int* __restrict__ row_pos, const int* __restrict__ row_slot,
-                       T* __restrict__ out, int nq, int window, float scale,
+                       T* __restrict__ out, int nq, int window, int keep_first, float scale,
                        const float* __restrict__ sink, const float* __restrict__ slopes) {
     pdl_prologue();
     const int d = cache.head_dim;
@@ -54,7 +55,11 @@ attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,
     }
     float m = -INFINITY, l = 0.0f;
     const float slope = slopes ? slopes[h] : 0.0f;
-    for (int j = lo; j <= pos; ++j) {
+    // with a window the first `keep_first` positions stay visible beyond it: they come
+    // first, then the window's keys, every key once and in the order of the positions
+    const int kept = keep_first < lo ? keep_first : lo;
+    for (int j = kept > 0 ? 0 : lo; j <= pos; ++j) {
+        if (j == kept && j < lo) j = lo;
         const size_t off = kv_offset(cache, slot, j, kvh);
         const T* kp = k_pages + off;
         const T* vp = v_pages + off;
@@ -101,7 +106,7 @@ attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,
 extern "C" int rfx_attention_plain(const void* q, const void* k_pages, const void* v_pages, int dt,
                                    const int* page_table, int max_pages, int page_size,
                                    const int* row_pos, const int* row_slot, void* out, int R,
-                                   int nq, int nkv, int head_dim, int window, float scale,
+                                   int nq, int nkv, int head_dim, int window, int keep_first, float scale,
                                    const float* sink, const float* slopes, void* stream) {
     if (R <= 0) return 0;
     if (head_dim <= 0 || head_dim > 32 * MAX_PER_LANE) return RFX_ERR_UNSUPPORTED;
@@ -113,11 +118,11 @@ extern "C" int rfx_attention_plain(const void* q, const void* k_pages, const voi
     if (dt == RFX_DT_F32)
         RFX_LAUNCH(attention_plain_kernel<float>, grid, 128, 0, s, (const float*)q,
                    (const float*)k_pages, (const float*)v_pages, cache, row_pos, row_slot,
-                   (float*)out, nq, window, scale, sink, slopes);
+                   (float*)out, nq, window, keep_first, scale, sink, slopes);
     else if (dt == RFX_DT_BF16)
         RFX_LAUNCH(attention_plain_kernel<__nv_bfloat16>, grid, 128, 0, s, (const __nv_bfloat16*)q,
                    (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, cache, row_pos,
-                   row_slot, (__nv_bfloat16*)out, nq, window, scale, sink, slopes);
+                   row_slot, (__nv_bfloat16*)out, nq, window, keep_first, scale, sink, slopes);
     else
         return RFX_ERR_BAD_ARG;
     return 0;

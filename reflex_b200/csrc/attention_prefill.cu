@@ -29,7 +29,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
                          const __nv_bfloat16* __restrict__ v_pages, PagedKV cache,
                          const int* __restrict__ seq_slot, const int* __restrict__ seq_start,
                          const int* __restrict__ seq_new, const int* __restrict__ seq_row0,
-                         __nv_bfloat16* __restrict__ out, int nq, int bq, int window,
+                         __nv_bfloat16* __restrict__ out, int nq, int bq, int window, int keep_first,
                          float scale_log2, const float* __restrict__ sink,
                          const float* __restrict__ slopes) {
     constexpr int LD = D + 8;
@@ -97,27 +97,33 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[n][i] = 0.0f;
 
-    const int pg0 = lo_tile / PAGE, pg1 = pos_last / PAGE + 1;
+    // The first `keep_first` positions stay visible beyond the window: the pages walked
+    // are those that hold such positions and lie before the window's first page, then
+    // the window's pages; entry pg of that list is page `logical(pg)` of the sequence.
+    const int first_page = lo_tile / PAGE;
+    const int kp = min((min(keep_first, lo_tile) + PAGE - 1) / PAGE, first_page);
+    auto logical = [&](int v) { return v < kp ? v : v - kp + first_page; };
+    const int pg0 = 0, pg1 = kp + pos_last / PAGE + 1 - first_page;
     // page ids are read one iteration ahead of their loads
-    issue(pg0, table[pg0], 0);
-    int page_ahead = pg0 + 1 < pg1 ? table[pg0 + 1] : 0;
+    issue(logical(pg0), table[logical(pg0)], 0);
+    int page_ahead = pg0 + 1 < pg1 ? table[logical(pg0 + 1)] : 0;
     for (int pg = pg0; pg < pg1; ++pg) {
         const int buf = (pg - pg0) & 1;
         if (pg + 1 < pg1) {
             const int page_now = page_ahead;
-            if (pg + 2 < pg1) page_ahead = table[pg + 2];
-            issue(pg + 1, page_now, buf ^ 1);
+            if (pg + 2 < pg1) page_ahead = table[logical(pg + 2)];
+            issue(logical(pg + 1), page_now, buf ^ 1);
             cp_async_wait<1>();
         } else {
             cp_async_wait<0>();
         }
         __syncthreads();
-        const int base = pg * PAGE;
-        // skip pages wholly after this warp's last query or before its window
-        if (warp_active && base <= warp_pos_max && base + PAGE > warp_lo) {
+        const int base = logical(pg) * PAGE;
+        // skip pages wholly after this warp's last query or before its window (kept ones stay)
+        if (warp_active && base <= warp_pos_max && (base + PAGE > warp_lo || base < keep_first)) {
             auto visible = [&](int key, int h) {
                 const int j = base + key;
-                return j <= row_pos[h] && j >= row_lo[h];
+                return j <= row_pos[h] && (j >= row_lo[h] || j < keep_first);
             };
             if (slopes) {
                 // a distance bias: slope * (query position - key position) off the score
@@ -152,7 +158,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
 template <int D>
 int launch_prefill(const void* q, const void* k_pages, const void* v_pages, const PagedKV& cache,
                    const int* seq_slot, const int* seq_start, const int* seq_new,
-                   const int* seq_row0, void* out, int S, int max_new, int nq, int window,
+                   const int* seq_row0, void* out, int S, int max_new, int nq, int window, int keep_first,
                    float scale, const float* sink, const float* slopes, cudaStream_t s) {
     constexpr int LD = D + 8;
     const int g = nq / cache.n_kv_heads;
@@ -166,7 +172,7 @@ int launch_prefill(const void* q, const void* k_pages, const void* v_pages, cons
     if (grid.y > 65535 || grid.z > 65535) return RFX_ERR_UNSUPPORTED;
     RFX_LAUNCH(kernel, grid, PF_THREADS, smem, s, (const __nv_bfloat16*)q,
                (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, cache, seq_slot, seq_start,
-               seq_new, seq_row0, (__nv_bfloat16*)out, nq, bq, window, scale * 1.4426950408889634f, sink, slopes);
+               seq_new, seq_row0, (__nv_bfloat16*)out, nq, bq, window, keep_first, scale * 1.4426950408889634f, sink, slopes);
     return 0;
 }
 
@@ -179,20 +185,23 @@ int launch_prefill(const void* q, const void* k_pages, const void* v_pages, cons
 // the softmax's denominator; slope * (query position - key position) is taken
 // off every score.
 // head_dim: multiples of 16 up to 256; group size nq / nkv up to 128; page 64.
-extern "C" int rfx_attention_prefill(const void* q, const void* k_pages, const void* v_pages,
-                                     const int* page_table, int max_pages, int page_size,
-                                     const int* seq_slot, const int* seq_start, const int* seq_new,
-                                     const int* seq_row0, void* out, int S, int max_new, int nq,
-                                     int nkv, int head_dim, int window, float scale, const float* sink,
-                                     const float* slopes, void* stream) {
+// `keep_first`: with a window, the first so many positions of a sequence stay visible
+// beyond it.
+extern "C" int rfx_attention_prefill_kf(const void* q, const void* k_pages, const void* v_pages,
+                                        const int* page_table, int max_pages, int page_size,
+                                        const int* seq_slot, const int* seq_start, const int* seq_new,
+                                        const int* seq_row0, void* out, int S, int max_new, int nq,
+                                        int nkv, int head_dim, int window, int keep_first, float scale,
+                                        const float* sink, const float* slopes, void* stream) {
     if (S <= 0 || max_new <= 0) return 0;
+    if (keep_first < 0) return RFX_ERR_BAD_ARG;
     if (page_size != PAGE || nkv <= 0 || nq % nkv != 0) return RFX_ERR_BAD_ARG;
     PagedKV cache{page_table, max_pages, page_size, nkv, head_dim};
     cudaStream_t s = (cudaStream_t)stream;
 #define RFX_CASE(DD)                                                                              \
     case DD:                                                                                      \
         return launch_prefill<DD>(q, k_pages, v_pages, cache, seq_slot, seq_start, seq_new,       \
-                                  seq_row0, out, S, max_new, nq, window, scale, sink, slopes, s);
+                                  seq_row0, out, S, max_new, nq, window, keep_first, scale, sink, slopes, s);
     switch (head_dim) {
         RFX_CASE(16) RFX_CASE(32) RFX_CASE(48) RFX_CASE(64) RFX_CASE(80) RFX_CASE(96)
         RFX_CASE(112) RFX_CASE(128) RFX_CASE(144) RFX_CASE(160) RFX_CASE(176) RFX_CASE(192)
@@ -201,4 +210,15 @@ extern "C" int rfx_attention_prefill(const void* q, const void* k_pages, const v
             return RFX_ERR_UNSUPPORTED;
     }
 #undef RFX_CASE
+}
+
+extern "C" int rfx_attention_prefill(const void* q, const void* k_pages, const void* v_pages,
+                                     const int* page_table, int max_pages, int page_size,
+                                     const int* seq_slot, const int* seq_start, const int* seq_new,
+                                     const int* seq_row0, void* out, int S, int max_new, int nq,
+                                     int nkv, int head_dim, int window, float scale, const float* sink,
+                                     const float* slopes, void* stream) {
+    return rfx_attention_prefill_kf(q, k_pages, v_pages, page_table, max_pages, page_size, seq_slot, seq_start,
+                                    seq_new, seq_row0, out, S, max_new, nq, nkv, head_dim, window, 0, scale, sink,
+                                    slopes, stream);
 }

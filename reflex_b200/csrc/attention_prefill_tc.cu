@@ -116,7 +116,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                             const __grid_constant__ CUtensorMap map_v, PagedKV cache,
                             const int* __restrict__ seq_slot, const int* __restrict__ seq_start,
                             const int* __restrict__ seq_new, const int* __restrict__ seq_row0,
-                            __nv_bfloat16* __restrict__ out, int nq, int bq, int window,
+                            __nv_bfloat16* __restrict__ out, int nq, int bq, int window, int keep_first,
                             float scale_log2, const float* __restrict__ sink,
                             const float* __restrict__ slopes, int* __restrict__ err) {
     static_assert(D == 64 || D == 128, "head sizes 64 and 128");
@@ -153,7 +153,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
     const int pos_first = start + q0, pos_last = pos_first + n_pos - 1;
     const int lo_tile = (window > 0 && pos_first + 1 > window) ? pos_first + 1 - window : 0;
     const int pg0 = lo_tile / PAGE, pg1 = active ? pos_last / PAGE + 1 : 0;
-    const int n_pages = active ? pg1 - pg0 : 0;
+    // The first `keep_first` positions stay visible beyond the window: the pages that hold
+    // such positions and lie before the window's first page are walked first, then the
+    // window's; entry j of that list is page `logical(j)` of the sequence.
+    const int kp = min((min(keep_first, lo_tile) + PAGE - 1) / PAGE, pg0);
+    auto logical = [&](int j) { return j < kp ? j : pg0 + j - kp; };
+    const int n_pages = active ? kp + pg1 - pg0 : 0;
 
     if (threadIdx.x == 0) {
         mbar_init(&q_full, 1);
@@ -193,7 +198,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
             for (int j = 0; j < n_pages; ++j) {
                 const int s = j % KV_STAGES;
                 const uint32_t ph = (j / KV_STAGES) & 1;
-                const int page = table[pg0 + j];
+                const int page = table[logical(j)];
                 const int y = (page * cache.n_kv_heads + kvh) * PAGE;
                 if (!mbar_wait(&k_empty[s], ph ^ 1)) { atomicExch(err, 11); abort_flag = 1; break; }
                 mbar_expect_tx(&k_full[s], KV_BYTES);
@@ -299,9 +304,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                 tmem_ld_16_nowait(tmem + lane_addr + S_COL + b * PAGE + c * 16, sr + c * 16);
             tmem_ld_wait();
 
-            const int basej = (pg0 + j) * PAGE;
+            const int basej = logical(j) * PAGE;
             // every key of the page visible to every valid row of the tile: no compares
-            const bool all_visible = basej + PAGE - 1 <= pos_first && basej >= lo_last && n_rows == ROWS;
+            const bool all_visible = basej + PAGE - 1 <= pos_first && (basej >= lo_last || basej + PAGE <= keep_first) &&
+                                     n_rows == ROWS;
             // four independent chains each for the maximum and the sum: one warp per
             // scheduler has nothing else to hide a dependent chain's latency with
             float s[PAGE];  // raw scores; the scale (positive) goes into the exponent's multiply-add
@@ -323,7 +329,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
 #pragma unroll
                 for (int c = 0; c < PAGE; ++c) {
                     const int key = basej + c;
-                    s[c] = (key <= row_pos && key >= row_lo) ? __uint_as_float(sr[c]) : -INFINITY;
+                    s[c] = (key <= row_pos && (key >= row_lo || key < keep_first)) ? __uint_as_float(sr[c]) : -INFINITY;
                     mx4[c & 3] = fmaxf(mx4[c & 3], s[c]);
                 }
             }
@@ -451,8 +457,8 @@ bool make_map_q(CUtensorMap* map, const void* base, int R, int nq, int D, int g,
 template <int D, bool SLOPES>
 int launch_tc(const void* q, const void* k_pages, const void* v_pages, long long n_pages_total,
               const PagedKV& cache, const int* seq_slot, const int* seq_start, const int* seq_new,
-              const int* seq_row0, void* out, int S, int max_new, int R, int nq, int window, float scale,
-              const float* sink, const float* slopes, int* err, cudaStream_t s) {
+              const int* seq_row0, void* out, int S, int max_new, int R, int nq, int window, int keep_first,
+              float scale, const float* sink, const float* slopes, int* err, cudaStream_t s) {
     const int g = nq / cache.n_kv_heads;
     if (g > ROWS) return RFX_ERR_UNSUPPORTED;
     const int bq = ROWS / g;
@@ -469,7 +475,7 @@ int launch_tc(const void* q, const void* k_pages, const void* v_pages, long long
     dim3 grid(cache.n_kv_heads, S, (max_new + bq - 1) / bq);
     if (grid.y > 65535 || grid.z > 65535) return RFX_ERR_UNSUPPORTED;
     RFX_LAUNCH(kernel, grid, THREADS, smem, s, mq, mk, mv, cache, seq_slot, seq_start, seq_new, seq_row0,
-               (__nv_bfloat16*)out, nq, bq, window, scale * 1.4426950408889634f, sink, slopes, err);
+               (__nv_bfloat16*)out, nq, bq, window, keep_first, scale * 1.4426950408889634f, sink, slopes, err);
     return 0;
 }
 
@@ -489,14 +495,17 @@ extern "C" int rfx_attention_prefill_tc_trace(void* buffer, int ctas) {
     return (int)e;
 }
 
-extern "C" int rfx_attention_prefill_tc(const void* q, const void* k_pages, const void* v_pages,
-                                        long long n_pages_total, const int* page_table, int max_pages,
-                                        int page_size, const int* seq_slot, const int* seq_start,
-                                        const int* seq_new, const int* seq_row0, void* out, int S,
-                                        int max_new, int R, int nq, int nkv, int head_dim, int window,
-                                        float scale, const float* sink, const float* slopes, int* err,
-                                        void* stream) {
+// `keep_first`: with a window, the first so many positions of a sequence stay visible
+// beyond it.
+extern "C" int rfx_attention_prefill_tc_kf(const void* q, const void* k_pages, const void* v_pages,
+                                           long long n_pages_total, const int* page_table, int max_pages,
+                                           int page_size, const int* seq_slot, const int* seq_start,
+                                           const int* seq_new, const int* seq_row0, void* out, int S,
+                                           int max_new, int R, int nq, int nkv, int head_dim, int window,
+                                           int keep_first, float scale, const float* sink, const float* slopes,
+                                           int* err, void* stream) {
     if (S <= 0 || max_new <= 0 || R <= 0) return 0;
+    if (keep_first < 0 || !(scale > 0.0f)) return RFX_ERR_UNSUPPORTED;  // the maximum is taken before the scale
     if (page_size != PAGE || nkv <= 0 || nq % nkv != 0) return RFX_ERR_BAD_ARG;
     if (slopes && !(scale > 0.0f)) return RFX_ERR_UNSUPPORTED;  // the slopes ride on the scale's multiply-add
     if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_pages) |
@@ -506,9 +515,21 @@ extern "C" int rfx_attention_prefill_tc(const void* q, const void* k_pages, cons
     cudaStream_t s = (cudaStream_t)stream;
 #define RFX_GO(DD, SL)                                                                                  \
     launch_tc<DD, SL>(q, k_pages, v_pages, n_pages_total, cache, seq_slot, seq_start, seq_new, seq_row0, \
-                      out, S, max_new, R, nq, window, scale, sink, slopes, err, s)
+                      out, S, max_new, R, nq, window, keep_first, scale, sink, slopes, err, s)
     if (head_dim == 64) return slopes ? RFX_GO(64, true) : RFX_GO(64, false);
     if (head_dim == 128) return slopes ? RFX_GO(128, true) : RFX_GO(128, false);
 #undef RFX_GO
     return RFX_ERR_UNSUPPORTED;
+}
+
+extern "C" int rfx_attention_prefill_tc(const void* q, const void* k_pages, const void* v_pages,
+                                        long long n_pages_total, const int* page_table, int max_pages,
+                                        int page_size, const int* seq_slot, const int* seq_start,
+                                        const int* seq_new, const int* seq_row0, void* out, int S,
+                                        int max_new, int R, int nq, int nkv, int head_dim, int window,
+                                        float scale, const float* sink, const float* slopes, int* err,
+                                        void* stream) {
+    return rfx_attention_prefill_tc_kf(q, k_pages, v_pages, n_pages_total, page_table, max_pages, page_size,
+                                       seq_slot, seq_start, seq_new, seq_row0, out, S, max_new, R, nq, nkv,
+                                       head_dim, window, 0, scale, sink, slopes, err, stream);
 }

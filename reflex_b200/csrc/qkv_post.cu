@@ -94,7 +94,7 @@ qkv_post_wide_kernel(const TI* __restrict__ qkv, int row_stride, const float* __
                      const float* __restrict__ rope_denom, int rotary_dim,
                      const int* __restrict__ row_pos, const int* __restrict__ row_slot,
                      TO* __restrict__ q_out, TO* __restrict__ k_pages, TO* __restrict__ v_pages,
-                     PagedKV cache, int nq, int nkv_in, int dry_pass, float magnitude) {
+                     PagedKV cache, int nq, int nkv_in, int dry_pass, float magnitude, int v_head0) {
     extern __shared__ float smem[];  // cos[half], sin[half]
     pdl_launch_dependents();
     constexpr int D = PER * LPH;
@@ -170,7 +170,7 @@ qkv_post_wide_kernel(const TI* __restrict__ qkv, int row_stride, const float* __
                 const int h = (k == 0 ? u : (k == 1 ? u - uq : u - uq - ukv)) * HPW + sub;
                 if (h < (k == 0 ? nq : nkv_in)) {
                     head[c] = h;
-                    const int hh = k == 0 ? h : (k == 1 ? nq + h : nq + nkv_in + h);
+                    const int hh = k == 0 ? h : (k == 1 ? nq + h : v_head0 + h);
                     const TI* src = dry ? dry_src : qkv + (size_t)r * row_stride + (size_t)hh * D;
                     in[c] = *reinterpret_cast<const Pack<TI, PER>*>(src + e0);
                 }
@@ -267,7 +267,7 @@ qkv_post_kernel(const TI* __restrict__ qkv, int row_stride, const float* __restr
                 const float* __restrict__ rope_denom, int rotary_dim,
                 const int* __restrict__ row_pos, const int* __restrict__ row_slot,
                 TO* __restrict__ q_out, TO* __restrict__ k_pages, TO* __restrict__ v_pages,
-                PagedKV cache, int nq, int nkv_in, int dry_pass, int pairing, float magnitude) {
+                PagedKV cache, int nq, int nkv_in, int dry_pass, int pairing, float magnitude, int v_head0) {
     extern __shared__ float smem[];  // [warps][head_dim], then cos[half], sin[half]
     pdl_launch_dependents();
     const int d = cache.head_dim;
@@ -316,8 +316,11 @@ qkv_post_kernel(const TI* __restrict__ qkv, int row_stride, const float* __restr
         // one warp per (row, head): blockIdx.y walks the heads in groups of nwarps
         for (int hh = blockIdx.y * nwarps + warp; hh < total; hh += stride) {
             if (dry && hh >= stride) break;
-            const TI* src = dry ? dry_src : qkv + (size_t)r * row_stride + (size_t)hh * d;
             const bool is_q = hh < nq, is_k = !is_q && hh < nq + nkv_in;
+            // a value head's columns start at head v_head0 of the row (the keys' own columns
+            // when the values are the keys as projected)
+            const int src_head = (is_q || is_k) ? hh : v_head0 + (hh - nq - nkv_in);
+            const TI* src = dry ? dry_src : qkv + (size_t)r * row_stride + (size_t)src_head * d;
             TO* dst = destination(hh);
             if (!is_q && !is_k) {  // v: stored as projected
                 for (int e = lane; e < d; e += 32)
@@ -385,13 +388,17 @@ qkv_post_kernel(const TI* __restrict__ qkv, int row_stride, const float* __restr
 
 }  // namespace
 
-extern "C" int rfx_qkv_post(const void* qkv, int in_dt, int row_stride, const float* q_w,
-                            const float* k_w, float eps, float w_offset, const float* rope_denom,
-                            int rotary_dim, const int* row_pos, const int* row_slot, void* q_out,
-                            void* k_pages, void* v_pages, int out_dt, const int* page_table,
-                            int max_pages, int page_size, int R, int nq, int nkv_in, int nkv,
-                            int head_dim, int pairing, float magnitude, void* stream) {
+// `values_are_keys`: the row holds no value columns; a value head is its key head as
+// projected (before the norm and the rotation).
+extern "C" int rfx_qkv_post_kv(const void* qkv, int in_dt, int row_stride, const float* q_w,
+                               const float* k_w, float eps, float w_offset, const float* rope_denom,
+                               int rotary_dim, const int* row_pos, const int* row_slot, void* q_out,
+                               void* k_pages, void* v_pages, int out_dt, const int* page_table,
+                               int max_pages, int page_size, int R, int nq, int nkv_in, int nkv,
+                               int head_dim, int pairing, float magnitude, int values_are_keys,
+                               void* stream) {
     if (R <= 0) return 0;
+    const int v_head0 = values_are_keys ? nq : nq + nkv_in;
     if (pairing != RFX_PAIR_HALF && pairing != RFX_PAIR_CONSECUTIVE) return RFX_ERR_BAD_ARG;
     if (head_dim <= 0 || head_dim > 32 * MAX_PER_LANE) return RFX_ERR_UNSUPPORTED;
     if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1)) return RFX_ERR_BAD_ARG;
@@ -429,7 +436,7 @@ extern "C" int rfx_qkv_post(const void* qkv, int in_dt, int row_stride, const fl
         dim3 grid(R, unit_blocks < 65535 ? unit_blocks : 65535);
         const size_t smem = (size_t)rotary_dim * sizeof(float);
 #define RFX_WIDE(TI, TO, P, L)                                                                    \
-    RFX_LAUNCH((qkv_post_wide_kernel<TI, TO, P, L>), grid, threads, smem, s, RFX_POST_ARGS(TI, TO), magnitude)
+    RFX_LAUNCH((qkv_post_wide_kernel<TI, TO, P, L>), grid, threads, smem, s, RFX_POST_ARGS(TI, TO), magnitude, v_head0)
 #define RFX_WIDE_32(TI, TO)  /* 32-bit input: 4 elements are 16 bytes */   \
     do {                                                                  \
         if (per == 4 && lph == 4) RFX_WIDE(TI, TO, 4, 4);                 \
@@ -464,11 +471,11 @@ extern "C" int rfx_qkv_post(const void* qkv, int in_dt, int row_stride, const fl
     dim3 grid(R, head_blocks < 65535 ? head_blocks : 65535);
 #define RFX_POST(TI, TO)                                                                              \
     do {                                                                                              \
-        if (head_dim <= 32) RFX_LAUNCH((qkv_post_kernel<TI, TO, 1>), grid, threads, smem, s, RFX_POST_ARGS(TI, TO), pairing, magnitude);        \
-        else if (head_dim <= 64) RFX_LAUNCH((qkv_post_kernel<TI, TO, 2>), grid, threads, smem, s, RFX_POST_ARGS(TI, TO), pairing, magnitude);   \
-        else if (head_dim <= 128) RFX_LAUNCH((qkv_post_kernel<TI, TO, 4>), grid, threads, smem, s, RFX_POST_ARGS(TI, TO), pairing, magnitude);  \
-        else if (head_dim <= 256) RFX_LAUNCH((qkv_post_kernel<TI, TO, 8>), grid, threads, smem, s, RFX_POST_ARGS(TI, TO), pairing, magnitude);  \
-        else RFX_LAUNCH((qkv_post_kernel<TI, TO, 16>), grid, threads, smem, s, RFX_POST_ARGS(TI, TO), pairing, magnitude);                      \
+        if (head_dim <= 32) RFX_LAUNCH((qkv_post_kernel<TI, TO, 1>), grid, threads, smem, s, RFX_POST_ARGS(TI, TO), pairing, magnitude, v_head0);        \
+        else if (head_dim <= 64) RFX_LAUNCH((qkv_post_kernel<TI, TO, 2>), grid, threads, smem, s, RFX_POST_ARGS(TI, TO), pairing, magnitude, v_head0);   \
+        else if (head_dim <= 128) RFX_LAUNCH((qkv_post_kernel<TI, TO, 4>), grid, threads, smem, s, RFX_POST_ARGS(TI, TO), pairing, magnitude, v_head0);  \
+        else if (head_dim <= 256) RFX_LAUNCH((qkv_post_kernel<TI, TO, 8>), grid, threads, smem, s, RFX_POST_ARGS(TI, TO), pairing, magnitude, v_head0);  \
+        else RFX_LAUNCH((qkv_post_kernel<TI, TO, 16>), grid, threads, smem, s, RFX_POST_ARGS(TI, TO), pairing, magnitude, v_head0);                      \
     } while (0)
     if (in_dt == RFX_DT_F32 && out_dt == RFX_DT_F32) RFX_POST(float, float);
     else if (in_dt == RFX_DT_F32 && out_dt == RFX_DT_BF16) RFX_POST(float, __nv_bfloat16);
@@ -477,4 +484,15 @@ extern "C" int rfx_qkv_post(const void* qkv, int in_dt, int row_stride, const fl
 #undef RFX_POST
 #undef RFX_POST_ARGS
     return 0;
+}
+
+extern "C" int rfx_qkv_post(const void* qkv, int in_dt, int row_stride, const float* q_w,
+                            const float* k_w, float eps, float w_offset, const float* rope_denom,
+                            int rotary_dim, const int* row_pos, const int* row_slot, void* q_out,
+                            void* k_pages, void* v_pages, int out_dt, const int* page_table,
+                            int max_pages, int page_size, int R, int nq, int nkv_in, int nkv,
+                            int head_dim, int pairing, float magnitude, void* stream) {
+    return rfx_qkv_post_kv(qkv, in_dt, row_stride, q_w, k_w, eps, w_offset, rope_denom, rotary_dim, row_pos,
+                           row_slot, q_out, k_pages, v_pages, out_dt, page_table, max_pages, page_size, R, nq,
+                           nkv_in, nkv, head_dim, pairing, magnitude, 0, stream);
 }

@@ -90,11 +90,14 @@ __device__ __forceinline__ float4 conv4_at(const float* __restrict__ proj, int l
     return y;
 }
 
+// y / (1 + e^-y), 32-bit
+__device__ __forceinline__ float silu_of(float y) { return y / (1.0f + expf(-y)); }
+
 __global__ void __launch_bounds__(256)
 short_conv_kernel(const float* __restrict__ proj, int ld, int col0, const float* __restrict__ bias,
                   const float* __restrict__ w, const float* __restrict__ cbias, int taps,
                   const float* __restrict__ state, size_t slot_stride, const int* __restrict__ row_slot,
-                  float* __restrict__ out, __nv_bfloat16* __restrict__ out_lo, int C, int by4) {
+                  float* __restrict__ out, __nv_bfloat16* __restrict__ out_lo, int C, int by4, int act) {
     pdl_prologue();
     const int r = blockIdx.x;
     const int before = rows_before(row_slot, r, taps - 1);
@@ -106,13 +109,15 @@ short_conv_kernel(const float* __restrict__ proj, int ld, int col0, const float*
                 const float4 cb = *reinterpret_cast<const float4*>(cbias + c);
                 y.x += cb.x; y.y += cb.y; y.z += cb.z; y.w += cb.w;
             }
+            if (act == 1) { y.x = silu_of(y.x); y.y = silu_of(y.y); y.z = silu_of(y.z); y.w = silu_of(y.w); }
             store4(out + (size_t)r * C + c, y);
             if (out_lo) store4(out_lo + (size_t)r * C + c, y);
         }
         return;
     }
     for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
-        const float y = conv_at(proj, ld, col0, c, bias, w, taps, tail, C, r, before) + (cbias ? cbias[c] : 0.0f);
+        float y = conv_at(proj, ld, col0, c, bias, w, taps, tail, C, r, before) + (cbias ? cbias[c] : 0.0f);
+        if (act == 1) y = silu_of(y);
         out[(size_t)r * C + c] = y;
         if (out_lo) out_lo[(size_t)r * C + c] = __float2bfloat16_rn(y);
     }
@@ -216,10 +221,13 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 
 
 // `w`: the filters transposed, [taps][C].  `out_lo` (may be null): the result once
 // more, rounded to bfloat16 (the input of a tensor-core product).
-extern "C" int rfx_short_conv(const float* proj, int ld, int col0, const float* bias, const float* w,
-                              const float* cbias, int taps, const float* state, long long slot_stride,
-                              const int* row_slot, float* out, void* out_lo, int R, int C, void* stream) {
+// `act`: 0 the convolution as it is, 1 silu of it (after `cbias`).
+extern "C" int rfx_short_conv_act(const float* proj, int ld, int col0, const float* bias, const float* w,
+                                  const float* cbias, int taps, const float* state, long long slot_stride,
+                                  const int* row_slot, float* out, void* out_lo, int R, int C, int act,
+                                  void* stream) {
     if (R <= 0 || C <= 0) return 0;
+    if (act != 0 && act != 1) return RFX_ERR_BAD_ARG;
     if (taps < 1 || taps > MAX_TAPS || (taps > 1 && !state)) return RFX_ERR_BAD_ARG;
     const int by4 = C % 4 == 0 && ld % 4 == 0 && col0 % 4 == 0 && slot_stride % 4 == 0 && aligned16(proj) &&
                     aligned16(bias) && aligned16(w) && aligned16(cbias) && aligned16(state) && aligned16(out) &&
@@ -228,8 +236,15 @@ extern "C" int rfx_short_conv(const float* proj, int ld, int col0, const float* 
     // so that a decode step's loads are all in flight at once
     dim3 grid(R, chunks(by4 ? C / (R >= 256 ? 8 : 4) : C, 256));
     RFX_LAUNCH(short_conv_kernel, grid, 256, 0, (cudaStream_t)stream, proj, ld, col0, bias, w, cbias, taps,
-               state, (size_t)slot_stride, row_slot, out, (__nv_bfloat16*)out_lo, C, by4);
+               state, (size_t)slot_stride, row_slot, out, (__nv_bfloat16*)out_lo, C, by4, act);
     return 0;
+}
+
+extern "C" int rfx_short_conv(const float* proj, int ld, int col0, const float* bias, const float* w,
+                              const float* cbias, int taps, const float* state, long long slot_stride,
+                              const int* row_slot, float* out, void* out_lo, int R, int C, void* stream) {
+    return rfx_short_conv_act(proj, ld, col0, bias, w, cbias, taps, state, slot_stride, row_slot, out, out_lo, R,
+                              C, 0, stream);
 }
 
 extern "C" int rfx_conv_qkv_post(const float* proj, int ld, const float* bias, const float* w, int taps,

@@ -168,6 +168,19 @@ __global__ void logit_finish_kernel(float* __restrict__ z, size_t n, float scale
     }
 }
 
+// a[r][c] <- a[r][c] * sigmoid(z[r][col + c]): a gate computed beside the values it
+// scales (columns of the same stacked product); the sigmoid is 32-bit
+template <typename TA, typename TZ>
+__global__ void __launch_bounds__(256)
+sigmoid_gate_mul_kernel(TA* __restrict__ a, const TZ* __restrict__ z, int ldz, int col, int H) {
+    pdl_prologue();
+    const size_t r = blockIdx.x;
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < H; c += gridDim.y * blockDim.x) {
+        const float g = ld<TZ>(z, r * ldz + col + c);
+        st<TA>(a, r * H + c, ld<TA>(a, r * H + c) / (1.0f + expf(-g)));
+    }
+}
+
 // blocks along a row for kernels that take a row's elements independently: few rows get a
 // thread an element (every load in flight at once), many rows walk their row
 int row_chunks(int R, int H) {
@@ -257,5 +270,23 @@ extern "C" int rfx_logit_finish(float* z, long long n, float scale, float cap, v
     if (n <= 0) return 0;
     RFX_LAUNCH(logit_finish_kernel, blocks_for((size_t)n), 256, 0, (cudaStream_t)stream, z, (size_t)n, scale,
                cap);
+    return 0;
+}
+
+extern "C" int rfx_sigmoid_gate_mul(void* a, int a_dt, const void* z, int z_dt, int ldz, int col, int R, int H,
+                                    void* stream) {
+    if (R <= 0 || H <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const dim3 grid(R, row_chunks(R, H));
+    if (a_dt == RFX_DT_F32 && z_dt == RFX_DT_F32)
+        RFX_LAUNCH((sigmoid_gate_mul_kernel<float, float>), grid, 256, 0, s, (float*)a, (const float*)z, ldz, col, H);
+    else if (a_dt == RFX_DT_BF16 && z_dt == RFX_DT_F32)
+        RFX_LAUNCH((sigmoid_gate_mul_kernel<__nv_bfloat16, float>), grid, 256, 0, s, (__nv_bfloat16*)a,
+                   (const float*)z, ldz, col, H);
+    else if (a_dt == RFX_DT_BF16 && z_dt == RFX_DT_BF16)
+        RFX_LAUNCH((sigmoid_gate_mul_kernel<__nv_bfloat16, __nv_bfloat16>), grid, 256, 0, s, (__nv_bfloat16*)a,
+                   (const __nv_bfloat16*)z, ldz, col, H);
+    else
+        return RFX_ERR_BAD_ARG;
     return 0;
 }

@@ -47,7 +47,7 @@ def expected_tensors(spec: ModelSpec) -> Dict[str, Tuple[Tuple[str, ...], Tensor
             out[name] = (("layer", str(li), part, role), info)
     if spec.stream_mix_name is not None:
         out[spec.stream_mix_name] = (("stream_mix",), TensorInfo((spec.hidden_size, 2 * spec.hidden_size), "matrix"))
-    out[spec.final_norm_name] = (("final_norm",), TensorInfo((spec.final_norm.size,), "norm"))
+    out[spec.final_norm_name] = (("final_norm",), NORMS.get(spec.final_norm.kind).tensor_specs(spec.final_norm)["weight"])
     if not spec.tie_word_embeddings:
         out[spec.head_name] = (("head",), TensorInfo((spec.vocab_size, spec.hidden_size), "matrix"))
     return out
@@ -66,6 +66,9 @@ class CausalLM:
         self.embedding: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
         self.stream_mix: Optional[torch.Tensor] = None
+        # a probe for tests and diagnostics: called after every layer run with (index,
+        # run, layer, hidden, pending); None in normal use
+        self.after_run = None
         if any(r.mixes_input for r in spec.run_order) and spec.stream_mix_name is None:
             raise ValueError("a run mixes its input but the model names no stream-mix matrix")
 
@@ -138,6 +141,9 @@ class CausalLM:
         for ti, term in enumerate(self.embedding_terms):
             entry = self.term_entry(ti)
             term.add(h, batch, cache.state(entry) if cache.has(entry) == "state" else None)
+        if self.spec.residual_streams > 1:
+            # the residual as several parallel copies: the embedding output into each
+            h = ops.hyper_expand(h, self.spec.residual_streams)
         ops.prof_mark("embed")
         pending = None
         order = self.spec.run_order
@@ -176,6 +182,13 @@ class CausalLM:
                 h, pending = layer.forward(h, pending, ctx, next_norm=next_norm)
             else:
                 h, pending = layer.forward(h, pending, ctx)
+            if self.after_run is not None:
+                self.after_run(i, run, layer, h, pending)
+        # a block arrangement that keeps the residual in a form of its own (several
+        # streams) hands back the ordinary one: [rows, hidden] and a delta or None
+        last = self.layers[order[-1].layer] if order else None
+        if last is not None and hasattr(last, "finish"):
+            h, pending = last.finish(h, pending)
         return h, pending
 
     def logits(self, hidden: torch.Tensor, pending, rows: torch.Tensor, rows_host=None) -> torch.Tensor:

@@ -275,7 +275,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
         native.check(st, f"gemm_f32 (R={R}, N={N}, K={K})")
         return y
     out_dtype = out_dtype or torch.bfloat16
-    if R <= GEMV_MAX_ROWS and K % 8 == 0:
+    if R <= GEMV_MAX_ROWS and K % 8 == 0 and (x.data_ptr() | weight.data_ptr()) % 16 == 0:
         return gemm_tc(x, weight, out_dtype, own=own)
     y = _new((R, N), out_dtype, x.device, own=own)
     if out_dtype == torch.float32:
@@ -377,10 +377,14 @@ def linear_swiglu(x: torch.Tensor, weight_pairs: torch.Tensor) -> torch.Tensor:
 def qkv_post(qkv: torch.Tensor, q_weight, k_weight, eps: float, weight_offset: float,
              rotation, row_pos: torch.Tensor, row_slot: torch.Tensor,
              k_pages, v_pages, page_table: torch.Tensor, page_size: int, nq: int, nkv: int,
-             head_dim: int, writes_cache: bool, out_dtype: torch.dtype) -> torch.Tensor:
+             head_dim: int, writes_cache: bool, out_dtype: torch.dtype, values_are_keys: bool = False,
+             ld: Optional[int] = None) -> torch.Tensor:
     """Per-head q/k norm, rotary encoding, q out, k and v into the cache.
     `rotation`: a `parts.Rotation` (denominators, rotary_dim, pairing,
-    magnitude) or None for no rotary encoding."""
+    magnitude) or None for no rotary encoding.  `values_are_keys`: the rows hold
+    no value columns; a value head is its key head as projected, before the norm
+    and the rotation.  `ld`: the rows are the first columns of a wider stacked
+    product (the row stride is then `qkv.shape[1]`, the q | k | v columns `ld`)."""
     from ..parts.registry import PAIRINGS
 
     R = qkv.shape[0]
@@ -393,17 +397,19 @@ def qkv_post(qkv: torch.Tensor, q_weight, k_weight, eps: float, weight_offset: f
         if rope_denom is not None and rope_denom.numel() != rotary_dim // 2:
             raise InvalidInput("qkv_post: one denominator per rotary pair is needed")
     nkv_in = nkv if writes_cache else 0
-    if qkv.shape[1] != (nq + 2 * nkv_in) * head_dim:
+    if (qkv.shape[1] if ld is None else ld) != (nq + (1 if values_are_keys else 2) * nkv_in) * head_dim:
         raise InvalidInput("qkv_post: qkv width does not match the head counts")
+    if ld is not None and ld > qkv.shape[1]:
+        raise InvalidInput("qkv_post: the q | k | v columns do not fit into the rows")
     q = _new((R, nq * head_dim), out_dtype, qkv.device)
-    st = native.lib().rfx_qkv_post(
+    st = native.lib().rfx_qkv_post_kv(
         _chk(qkv, "qkv"), dt_code(qkv.dtype), qkv.shape[1], _chk(q_weight, "q_norm", torch.float32),
         _chk(k_weight, "k_norm", torch.float32), float(eps), float(weight_offset),
         _chk(rope_denom, "rope_denom", torch.float32), int(rotary_dim),
         _chk(row_pos, "row_pos", torch.int32), _chk(row_slot, "row_slot", torch.int32),
         q.data_ptr(), _chk(k_pages, "k_pages"), _chk(v_pages, "v_pages"), dt_code(out_dtype),
         _chk(page_table, "page_table", torch.int32), page_table.shape[1], page_size, R, nq, nkv_in,
-        nkv, head_dim, pairing, magnitude, _stream())
+        nkv, head_dim, pairing, magnitude, 1 if values_are_keys else 0, _stream())
     native.check(st, f"qkv_post (head_dim={head_dim})")
     return q
 
@@ -473,8 +479,9 @@ def attention_plain(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
                     row_slot: torch.Tensor, nq: int, nkv: int, head_dim: int,
                     window: Optional[int], scale: float,
                     sink: Optional[torch.Tensor] = None,
-                    slopes: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """`sink` (float32, one per query head): exp(sink) joins the softmax's
+                    slopes: Optional[torch.Tensor] = None, keep_first: int = 0) -> torch.Tensor:
+    """`keep_first`: with a window, the first so many positions of a sequence
+    stay visible beyond it.  `sink` (float32, one per query head): exp(sink) joins the softmax's
     denominator once, with no key and no value.  `slopes` (float32, one per
     query head): slope * (query position - key position) is taken off every
     score, a linear distance bias."""
@@ -484,7 +491,7 @@ def attention_plain(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
         _chk(q, "q"), _chk(k_pages, "k_pages", q.dtype), _chk(v_pages, "v_pages", q.dtype),
         dt_code(q.dtype), _chk(page_table, "page_table", torch.int32), page_table.shape[1],
         page_size, _chk(row_pos, "row_pos", torch.int32), _chk(row_slot, "row_slot", torch.int32),
-        out.data_ptr(), R, nq, nkv, head_dim, int(window or 0), float(scale),
+        out.data_ptr(), R, nq, nkv, head_dim, int(window or 0), int(keep_first if window else 0), float(scale),
         _chk(sink, "sink", torch.float32), _chk(slopes, "slopes", torch.float32), _stream())
     native.check(st, f"attention_plain (head_dim={head_dim})")
     return out
@@ -556,9 +563,10 @@ def decode_splits(n_rows: int, nq: int, nkv: int, max_pages: int = 64) -> int:
 def attention_decode(q, k_pages, v_pages, page_table, page_size, row_pos, row_slot, nq, nkv,
                      head_dim, window, scale, n_splits: Optional[int] = None,
                      sink: Optional[torch.Tensor] = None,
-                     slopes: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     slopes: Optional[torch.Tensor] = None, keep_first: int = 0) -> torch.Tensor:
     """bfloat16 tensor-core attention for rows that are each one query
     position (decode), split over the keys."""
+    keep_first = int(keep_first) if window else 0
     R = q.shape[0]
     _chk(q, "q", torch.bfloat16)
     if head_dim % 16 or not (16 <= head_dim <= 256):
@@ -570,23 +578,24 @@ def attention_decode(q, k_pages, v_pages, page_table, page_size, row_pos, row_sl
                                            and v_pages.is_contiguous() and v_pages.shape == k_pages.shape) else 0
     if CLUSTER_MERGE and n_splits in (2, 4, 8, 16):
         # the splits as one thread-block cluster that merges its partials itself
-        st = native.lib().rfx_attention_decode_cluster(
+        st = native.lib().rfx_attention_decode_kf(
             q.data_ptr(), _chk(k_pages, "k_pages", torch.bfloat16), _chk(v_pages, "v_pages", torch.bfloat16),
             _chk(page_table, "page_table", torch.int32), page_table.shape[1], page_size,
-            _chk(row_pos, "row_pos", torch.int32), _chk(row_slot, "row_slot", torch.int32), out.data_ptr(),
-            R, nq, nkv, head_dim, n_splits, int(window or 0), float(scale), _chk(sink, "sink", torch.float32),
-            _chk(slopes, "slopes", torch.float32), pool_pages, device_error_word(q.device).data_ptr(), _stream())
+            _chk(row_pos, "row_pos", torch.int32), _chk(row_slot, "row_slot", torch.int32), out.data_ptr(), 0,
+            R, nq, nkv, head_dim, n_splits, int(window or 0), keep_first, float(scale),
+            _chk(sink, "sink", torch.float32), _chk(slopes, "slopes", torch.float32), pool_pages, 1,
+            device_error_word(q.device).data_ptr(), _stream())
         if st != native.ERR_UNSUPPORTED:
             native.check(st, f"attention_decode_cluster (head_dim={head_dim}, splits={n_splits})")
             return out
     partial = _new((R * nq * n_splits * (head_dim + 2),), torch.float32, q.device) if n_splits > 1 else None
-    st = native.lib().rfx_attention_decode(
+    st = native.lib().rfx_attention_decode_kf(
         q.data_ptr(), _chk(k_pages, "k_pages", torch.bfloat16), _chk(v_pages, "v_pages", torch.bfloat16),
         _chk(page_table, "page_table", torch.int32), page_table.shape[1], page_size,
         _chk(row_pos, "row_pos", torch.int32), _chk(row_slot, "row_slot", torch.int32), out.data_ptr(),
         partial.data_ptr() if partial is not None else 0, R, nq, nkv, head_dim, n_splits,
-        int(window or 0), float(scale), _chk(sink, "sink", torch.float32),
-        _chk(slopes, "slopes", torch.float32), pool_pages, device_error_word(q.device).data_ptr(), _stream())
+        int(window or 0), keep_first, float(scale), _chk(sink, "sink", torch.float32),
+        _chk(slopes, "slopes", torch.float32), pool_pages, 0, device_error_word(q.device).data_ptr(), _stream())
     native.check(st, f"attention_decode (head_dim={head_dim}, splits={n_splits})")
     return out
 
@@ -596,7 +605,7 @@ CLUSTER_MERGE = _env_flag("REFLEX_B200_CLUSTER_MERGE", True)
 
 def attention_prefill(q, k_pages, v_pages, page_table, page_size, seq_slot, seq_start, seq_new,
                       seq_row0, max_new: int, nq, nkv, head_dim, window, scale, sink=None,
-                      slopes=None) -> torch.Tensor:
+                      slopes=None, keep_first: int = 0) -> torch.Tensor:
     """bfloat16 tensor-core attention for a packed batch of sequences that
     each bring one or more rows (prefill, chunks, mixed steps)."""
     _chk(q, "q", torch.bfloat16)
@@ -606,12 +615,12 @@ def attention_prefill(q, k_pages, v_pages, page_table, page_size, seq_slot, seq_
         raise InvalidInput(f"attention_prefill takes up to 128 query heads per kv head, got {nq // nkv}")
     out = _new(q.shape, q.dtype, q.device)
     S = seq_slot.numel()
-    st = native.lib().rfx_attention_prefill(
+    st = native.lib().rfx_attention_prefill_kf(
         q.data_ptr(), _chk(k_pages, "k_pages", torch.bfloat16), _chk(v_pages, "v_pages", torch.bfloat16),
         _chk(page_table, "page_table", torch.int32), page_table.shape[1], page_size,
         _chk(seq_slot, "seq_slot", torch.int32), _chk(seq_start, "seq_start", torch.int32),
         _chk(seq_new, "seq_new", torch.int32), _chk(seq_row0, "seq_row0", torch.int32), out.data_ptr(),
-        S, int(max_new), nq, nkv, head_dim, int(window or 0), float(scale),
+        S, int(max_new), nq, nkv, head_dim, int(window or 0), int(keep_first) if window else 0, float(scale),
         _chk(sink, "sink", torch.float32), _chk(slopes, "slopes", torch.float32), _stream())
     native.check(st, f"attention_prefill (head_dim={head_dim})")
     return out
@@ -619,7 +628,7 @@ def attention_prefill(q, k_pages, v_pages, page_table, page_size, seq_slot, seq_
 
 def attention_prefill_tc(q, k_pages, v_pages, page_table, page_size, seq_slot, seq_start, seq_new,
                          seq_row0, max_new: int, nq, nkv, head_dim, window, scale, sink=None,
-                         slopes=None) -> torch.Tensor:
+                         slopes=None, keep_first: int = 0) -> torch.Tensor:
     """The tcgen05/TMEM form of `attention_prefill`, for head sizes 64 and 128
     (with `slopes` the scale must be positive)."""
     _chk(q, "q", torch.bfloat16)
@@ -628,12 +637,13 @@ def attention_prefill_tc(q, k_pages, v_pages, page_table, page_size, seq_slot, s
     if nq // nkv > 128:
         raise InvalidInput(f"attention_prefill_tc takes up to 128 query heads per kv head, got {nq // nkv}")
     out = _new(q.shape, q.dtype, q.device)
-    st = native.lib().rfx_attention_prefill_tc(
+    st = native.lib().rfx_attention_prefill_tc_kf(
         q.data_ptr(), _chk(k_pages, "k_pages", torch.bfloat16), _chk(v_pages, "v_pages", torch.bfloat16),
         k_pages.shape[0], _chk(page_table, "page_table", torch.int32), page_table.shape[1], page_size,
         _chk(seq_slot, "seq_slot", torch.int32), _chk(seq_start, "seq_start", torch.int32),
         _chk(seq_new, "seq_new", torch.int32), _chk(seq_row0, "seq_row0", torch.int32), out.data_ptr(),
-        seq_slot.numel(), int(max_new), q.shape[0], nq, nkv, head_dim, int(window or 0), float(scale),
+        seq_slot.numel(), int(max_new), q.shape[0], nq, nkv, head_dim, int(window or 0),
+        int(keep_first) if window else 0, float(scale),
         _chk(sink, "sink", torch.float32), _chk(slopes, "slopes", torch.float32),
         device_error_word(q.device).data_ptr(), _stream())
     native.check(st, f"attention_prefill_tc (head_dim={head_dim})")
@@ -641,28 +651,32 @@ def attention_prefill_tc(q, k_pages, v_pages, page_table, page_size, seq_slot, s
 
 
 def attention(q, k_pages, v_pages, page_table, page_size, batch, nq, nkv, head_dim, window, scale,
-              sink=None, slopes=None):
+              sink=None, slopes=None, keep_first: int = 0):
     """Attention of the step's rows over their sequences' cached keys and
     values; picks the kernel for the dtype and the kind of step.  `sink`: one
     float32 per query head whose exponential joins the softmax's denominator.
     `slopes`: one float32 per query head; slope * (query position - key
-    position) is taken off every score."""
+    position) is taken off every score.  `keep_first`: with a window, the first
+    so many positions of a sequence stay visible beyond it."""
     fast = q.dtype == torch.bfloat16 and head_dim % 16 == 0 and head_dim <= 256
+    keep_first = int(keep_first) if window else 0
     if fast and batch.is_decode:
         pages = -(-min(batch.max_context, window or batch.max_context) // page_size) + (1 if window else 0)
+        pages += -(-keep_first // page_size)
         return attention_decode(q, k_pages, v_pages, page_table, page_size, batch.row_pos,
                                 batch.row_slot, nq, nkv, head_dim, window, scale,
-                                n_splits=decode_splits(q.shape[0], nq, nkv, pages), sink=sink, slopes=slopes)
-    if fast and nq // nkv <= 128 and head_dim in (64, 128) and (slopes is None or scale > 0):
+                                n_splits=decode_splits(q.shape[0], nq, nkv, pages), sink=sink, slopes=slopes,
+                                keep_first=keep_first)
+    if fast and nq // nkv <= 128 and head_dim in (64, 128) and scale > 0:
         return attention_prefill_tc(q, k_pages, v_pages, page_table, page_size, batch.seq_slot,
                                     batch.seq_start, batch.seq_new, batch.seq_row0, batch.max_new, nq,
-                                    nkv, head_dim, window, scale, sink, slopes)
+                                    nkv, head_dim, window, scale, sink, slopes, keep_first)
     if fast and nq // nkv <= 128:
         return attention_prefill(q, k_pages, v_pages, page_table, page_size, batch.seq_slot,
                                  batch.seq_start, batch.seq_new, batch.seq_row0, batch.max_new, nq,
-                                 nkv, head_dim, window, scale, sink, slopes)
+                                 nkv, head_dim, window, scale, sink, slopes, keep_first)
     return attention_plain(q, k_pages, v_pages, page_table, page_size, batch.row_pos,
-                           batch.row_slot, nq, nkv, head_dim, window, scale, sink, slopes)
+                           batch.row_slot, nq, nkv, head_dim, window, scale, sink, slopes, keep_first)
 
 
 # ------------------------------------------------- further norms and embedding terms
@@ -1075,26 +1089,30 @@ def branch_norm_mean(a: torch.Tensor, a_bias: Optional[torch.Tensor], wa: torch.
 
 # ------------------------------------------- short convolutions, gated recurrence
 def short_conv(proj: torch.Tensor, col0: int, channels: int, bias: Optional[torch.Tensor], filters_t: torch.Tensor,
-               conv_bias: Optional[torch.Tensor], state: Optional[torch.Tensor], batch, also_bf16: bool = False):
+               conv_bias: Optional[torch.Tensor], state: Optional[torch.Tensor], batch, also_bf16: bool = False,
+               activation: Optional[str] = None):
     """A causal convolution over time of columns [col0, col0 + channels) of
     `proj` (float32 [R, ld]) plus `bias`, one filter a channel (`filters_t`
     float32 [taps, channels], transposed; the last tap on the current token)
     plus `conv_bias`; what lies before a step's rows comes from `state` ([slots,
     n] float32, whose first (taps - 1) * channels floats are the sequence's last
     inputs, oldest first).  float32 [R, channels]; with `also_bf16` a pair, the
-    second the same values rounded to bfloat16."""
+    second the same values rounded to bfloat16.  `activation` "silu": y / (1 +
+    e^-y) of the result (after `conv_bias`)."""
+    if activation not in (None, "silu"):
+        raise InvalidInput(f"short_conv: activation must be None or 'silu', got {activation!r}")
     R = proj.shape[0]
     taps = filters_t.shape[0]
     if filters_t.shape[1] != channels:
         raise InvalidInput("short_conv: the filters must be [taps, channels]")
     out = _new((R, channels), torch.float32, proj.device)
     lo = _new((R, channels), torch.bfloat16, proj.device) if also_bf16 else None
-    st = native.lib().rfx_short_conv(
+    st = native.lib().rfx_short_conv_act(
         _chk(proj, "proj", torch.float32), proj.shape[1], int(col0), _chk(bias, "bias", torch.float32),
         _chk(filters_t, "filters_t", torch.float32), _chk(conv_bias, "conv_bias", torch.float32), taps,
         _chk(state, "state", torch.float32), state.stride(0) if state is not None else 0,
         _chk(batch.row_slot, "row_slot", torch.int32), out.data_ptr(), lo.data_ptr() if lo is not None else 0,
-        R, channels, _stream())
+        R, channels, 1 if activation == "silu" else 0, _stream())
     native.check(st, f"short_conv (taps={taps})")
     return (out, lo) if also_bf16 else out
 
@@ -1171,6 +1189,119 @@ def rglru_scan(u: torch.Tensor, gates: torch.Tensor, r_bias, i_bias, lam: torch.
         batch.seq_slot.numel(), out.data_ptr(), dt_code(out_dtype), W, int(blocks), 1 if chunked else 0,
         int(x_off), _chk(x_bias, "x_bias", torch.float32), int(taps), int(tail_off), _stream())
     native.check(st, f"rglru_scan (width={W}, blocks={blocks})")
+    return out
+
+
+# -------------------------------------------------------- several residual streams
+def hyper_expand(x: torch.Tensor, streams: int) -> torch.Tensor:
+    """The embedding output [R, W] copied into every one of `streams` residual
+    streams, float32 [R, streams * W]; lives for the whole step."""
+    R, W = x.shape
+    out = _new((R, streams * W), torch.float32, x.device, keep=True)
+    st = native.lib().rfx_hyper_expand(_chk(x, "x", torch.float32), out.data_ptr(), R, int(streams), W, _stream())
+    native.check(st, f"hyper_expand (streams={streams})")
+    return out
+
+
+class StreamWrite:
+    """A sublayer's result that still has to go into the residual streams:
+    x_t <- sum_s mix[s, t] x_s + out[t] * (scale * y), with `y` [R, W], `scale`
+    float32 [W] or None, `mix` float32 [S, S] (from, to), `out` float32 [S]."""
+
+    def __init__(self, y: torch.Tensor, scale: Optional[torch.Tensor], mix: torch.Tensor, out: torch.Tensor):
+        self.y, self.scale, self.mix, self.out = y, scale, mix, out
+
+
+def hyper_step(streams: torch.Tensor, write: Optional["StreamWrite"], read: torch.Tensor, norm_weight: torch.Tensor,
+               eps: float, weight_offset: float, out_dtype: torch.dtype, n_streams: int) -> torch.Tensor:
+    """`streams` float32 [R, S * W], updated in place by `write` (if any); then
+    u = sum_s read[s] x_s and its RMS norm, u / sqrt(mean(u^2) + eps) *
+    (weight_offset + norm_weight), [R, W] in `out_dtype`: one launch."""
+    R = streams.shape[0]
+    S = int(n_streams)
+    W = streams.shape[1] // S
+    out = _new((R, W), out_dtype, streams.device)
+    y = write.y if write is not None else None
+    if y is not None and tuple(y.shape) != (R, W):
+        raise InvalidInput("hyper_step: the sublayer's result must be [rows, width]")
+    st = native.lib().rfx_hyper_step(
+        _chk(streams, "streams", torch.float32), _chk(y, "y"), dt_code(y.dtype) if y is not None else 0,
+        _chk(write.scale, "scale", torch.float32) if write is not None else 0,
+        _chk(write.mix, "mix", torch.float32) if write is not None else 0,
+        _chk(write.out, "out", torch.float32) if write is not None else 0,
+        _chk(read, "read", torch.float32), _chk(norm_weight, "norm_weight", torch.float32), float(eps),
+        float(weight_offset), out.data_ptr(), dt_code(out_dtype), R, S, W, _stream())
+    native.check(st, f"hyper_step (streams={S}, width={W})")
+    return out
+
+
+def hyper_collapse(streams: torch.Tensor, write: Optional["StreamWrite"], n_streams: int) -> torch.Tensor:
+    """The sum of the residual streams after `write` (if any), float32 [R, W];
+    `streams` itself is left as it is."""
+    R = streams.shape[0]
+    S = int(n_streams)
+    W = streams.shape[1] // S
+    out = _new((R, W), torch.float32, streams.device, keep=True)
+    y = write.y if write is not None else None
+    st = native.lib().rfx_hyper_collapse(
+        _chk(streams, "streams", torch.float32), _chk(y, "y"), dt_code(y.dtype) if y is not None else 0,
+        _chk(write.scale, "scale", torch.float32) if write is not None else 0,
+        _chk(write.mix, "mix", torch.float32) if write is not None else 0,
+        _chk(write.out, "out", torch.float32) if write is not None else 0, out.data_ptr(), R, S, W, _stream())
+    native.check(st, f"hyper_collapse (streams={S}, width={W})")
+    return out
+
+
+# ------------------------------------------------------------ gates, activations
+def sigmoid_gate_mul_(a: torch.Tensor, z: torch.Tensor, col: int) -> torch.Tensor:
+    """a[r, c] *= sigmoid(z[r, col + c]), in place; the sigmoid is 32-bit."""
+    R, H = a.shape
+    if col < 0 or col + H > z.shape[1] or z.shape[0] != R:
+        raise InvalidInput("sigmoid_gate_mul: the gate's columns do not fit into z")
+    st = native.lib().rfx_sigmoid_gate_mul(_chk(a, "a"), dt_code(a.dtype), _chk(z, "z"), dt_code(z.dtype),
+                                           z.shape[1], int(col), R, H, _stream())
+    native.check(st, "sigmoid_gate_mul")
+    return a
+
+
+def relu2_(a: torch.Tensor) -> torch.Tensor:
+    """a <- max(a, 0)^2, in place."""
+    st = native.lib().rfx_moe_activation(_chk(a, "a"), dt_code(a.dtype), a.numel(), MOE_ACTIVATIONS["relu2"],
+                                         _stream())
+    native.check(st, "relu2")
+    return a
+
+
+def linear_relu2(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """relu(x @ W.T)^2, [R, I] in x's dtype: product, then the activation in place."""
+    return relu2_(linear(x, weight))
+
+
+# ------------------------------------------------------------- selective scan
+def mamba_scan(x: torch.Tensor, dtpre: torch.Tensor, dt_bias: Optional[torch.Tensor], bc: torch.Tensor, b_off: int,
+               c_off: int, z: torch.Tensor, z_off: int, A: torch.Tensor, D: Optional[torch.Tensor],
+               state: torch.Tensor, state_off: int, batch, out_dtype: torch.dtype) -> torch.Tensor:
+    """The selective scan over the step's rows, sequence by sequence
+    (csrc/mamba.cu): `x`, `dtpre` float32 [R, channels]; `bc` float32 rows with B
+    at column `b_off` and C at `c_off` (N each); `z` float32 rows with the gate's
+    pre-activation at `z_off`; `A` float32 [channels, N]; the running state is
+    `state[slot, state_off : state_off + channels * N]`.  Returns (S . C + D x) *
+    silu(z), [R, channels] in `out_dtype`."""
+    R, C = x.shape
+    N = A.shape[1]
+    if tuple(dtpre.shape) != (R, C) or A.shape[0] != C:
+        raise InvalidInput("mamba_scan: x and dtpre must be [rows, channels] and A [channels, states]")
+    if max(b_off, c_off) + N > bc.shape[1] or z_off + C > z.shape[1]:
+        raise InvalidInput("mamba_scan: B, C or z do not fit into their rows")
+    out = _new((R, C), out_dtype, x.device)
+    st = native.lib().rfx_mamba_scan(
+        _chk(x, "x", torch.float32), _chk(dtpre, "dtpre", torch.float32), _chk(dt_bias, "dt_bias", torch.float32),
+        _chk(bc, "bc", torch.float32), bc.shape[1], int(b_off), int(c_off), _chk(z, "z", torch.float32),
+        z.shape[1], int(z_off), _chk(A, "A", torch.float32), _chk(D, "D", torch.float32),
+        _chk(state, "state", torch.float32), state.stride(0), int(state_off),
+        _chk(batch.seq_slot, "seq_slot", torch.int32), _chk(batch.seq_row0, "seq_row0", torch.int32),
+        batch.seq_slot.numel(), out.data_ptr(), dt_code(out_dtype), C, N, _stream())
+    native.check(st, f"mamba_scan (channels={C}, states={N})")
     return out
 
 

@@ -42,8 +42,31 @@ _SIGNATURES = {
                      c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
                      c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
     "rfx_attention_plain": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p,
-                            c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p,
+                            c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p,
                             c_void_p],
+    "rfx_attention_decode_kf": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
+                                c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                                c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p],
+    "rfx_attention_prefill_kf": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
+                                 c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                 c_float, c_void_p, c_void_p, c_void_p],
+    "rfx_attention_prefill_tc_kf": [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_int, c_void_p,
+                                    c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                    c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p],
+    "rfx_qkv_post_kv": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_float, c_float, c_void_p, c_int,
+                        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
+                        c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+    "rfx_short_conv_act": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_longlong,
+                           c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "rfx_sigmoid_gate_mul": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "rfx_hyper_expand": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "rfx_hyper_step": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float,
+                       c_float, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "rfx_hyper_collapse": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                           c_void_p],
+    "rfx_mamba_scan": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int,
+                       c_void_p, c_void_p, c_void_p, c_longlong, c_longlong, c_void_p, c_void_p, c_int, c_void_p,
+                       c_int, c_int, c_int, c_void_p],
     "rfx_attention_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
                              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
                              c_void_p, c_longlong, c_void_p, c_void_p],

@@ -9,6 +9,13 @@ softmax((q . k_j) * scale) in 32-bit, weighted sum of v_j; out = attn Wo^T
 The q, k, v weights are stacked into one matrix at load; the reference fuses
 the three products by kernel instead (src/kernels_cuda/gemv_fused.cu:16-87).
 
+Options, by the spec's parameters: `values_are_keys` (there is no Wv; a value
+head is its key head as projected, before the norm and the rotation),
+`output_gate` (a further matrix Wg; the concatenated heads are multiplied by
+sigmoid(x Wg^T) before Wo) and `keep_first` (with a window: the first so many
+positions of a sequence stay visible to every later query, i - j < window or
+j < keep_first, and keep their own positions).
+
 The part knows sizes only from its spec.  What it needs from the step is in
 `ctx`: row positions, row slots, and the cache entry's pages and page table.
 """
@@ -26,6 +33,12 @@ from ..errors import InvalidInput
 from .registry import NORMS, POSITIONS, TensorInfo, register_mixer
 
 
+def any_reader(spec: MixerSpec) -> bool:
+    """Whether a run of this mixer may read another run's keys and values (it then
+    needs its query and gate rows apart from the key and value rows)."""
+    return bool(spec.param("shares_cache", False))
+
+
 @register_mixer("gqa_attention")
 class GQAttention:
     def __init__(self, spec: MixerSpec, dtype: torch.dtype, device):
@@ -39,6 +52,9 @@ class GQAttention:
             if spec.position is not None
             else None
         )
+        self.values_are_keys = bool(spec.param("values_are_keys", False))
+        self.output_gate = bool(spec.param("output_gate", False))
+        self.keep_first = int(spec.param("keep_first", 0) or 0) if spec.window else 0
         self.qkv = None
         self.q_only = None
         self.o = None
@@ -54,23 +70,35 @@ class GQAttention:
             "v_proj": TensorInfo((spec.num_kv_heads * d, H), "matrix"),
             "o_proj": TensorInfo((H, spec.num_heads * d), "matrix"),
         }
+        if spec.param("values_are_keys", False):
+            del out["v_proj"]
+        if spec.param("output_gate", False):
+            out["g_proj"] = TensorInfo((spec.num_heads * d, H), "matrix")
         if spec.qk_norm is not None:
             out["q_norm"] = TensorInfo((d,), "norm")
             out["k_norm"] = TensorInfo((d,), "norm")
         return out
 
     def cache_spec(self) -> KVSpec:
-        return KVSpec(self.spec.num_kv_heads, self.spec.head_dim, self.spec.window)
+        return KVSpec(self.spec.num_kv_heads, self.spec.head_dim, self.spec.window, keep_first=self.keep_first)
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         def dev(t):
             return t.to(device=self.device, dtype=self.dtype)
 
         q = dev(tensors["q_proj"])
-        self.qkv = torch.cat([q, dev(tensors["k_proj"]), dev(tensors["v_proj"])], dim=0).contiguous()
+        stack = [q, dev(tensors["k_proj"])]
+        if not self.values_are_keys:
+            stack.append(dev(tensors["v_proj"]))
+        self.kv_cols = sum(t.shape[0] for t in stack)  # the q | k | v columns of the stacked product
+        if self.output_gate:
+            stack.append(dev(tensors["g_proj"]))  # the gate's columns ride in the same product
+        self.qkv = torch.cat(stack, dim=0).contiguous()
         # rows [0, nq*d) of the stacked matrix: the query part, for runs that
         # read another run's keys and values
         self.q_only = self.qkv[: q.shape[0]]
+        self.q_gate = (torch.cat([q, dev(tensors["g_proj"])], dim=0).contiguous()
+                       if self.output_gate and any_reader(self.spec) else None)
         self.o = dev(tensors["o_proj"]).contiguous()
         if self.spec.qk_norm is not None:
             self.q_norm = tensors["q_norm"].to(device=self.device, dtype=torch.float32).contiguous()
@@ -97,6 +125,8 @@ class GQAttention:
         w = self.qkv if ctx.writes_cache else self.q_only
         rotation = None if self.position is None else self.position.rotation()
         norm = s.qk_norm
+        if self.values_are_keys or self.output_gate or self.keep_first:
+            return self._forward_general(x, ctx, rotation)
         if ops.qkv_fused_takes(x, s.head_dim, rotation, w):
             # a few rows: norms, rotation and the cache write are the product's epilogue
             q = ops.qkv_fused(
@@ -122,6 +152,39 @@ class GQAttention:
             if fused is not None:
                 ops.prof_mark("o_proj")
                 return None if fused is ops.ADDED else fused  # None: nothing left to add
+        out = ops.linear(attn, self.o, out_dtype=torch.float32)
+        ops.prof_mark("o_proj")
+        return out
+
+    def _forward_general(self, x, ctx, rotation):
+        """The form with any of the options: one stacked product [q | k | (v) | (gate)],
+        `qkv_post` on its first columns, the attention, the gate, the output
+        projection; the delta [rows, hidden] comes back 32-bit."""
+        s, kv, batch, norm = self.spec, ctx.kv, ctx.batch, self.spec.qk_norm
+        if isinstance(x, ops.NormedInput):
+            raise InvalidInput("gqa_attention: this form takes plain normed rows")
+        nq_cols = s.num_heads * s.head_dim
+        if ctx.writes_cache:
+            w, cols, gate_col = self.qkv, self.kv_cols, self.kv_cols
+        elif self.output_gate:
+            if self.q_gate is None:
+                raise InvalidInput("gqa_attention: a run that reads another's cache needs `shares_cache` in its spec")
+            w, cols, gate_col = self.q_gate, nq_cols, nq_cols
+        else:
+            w, cols, gate_col = self.q_only, nq_cols, nq_cols
+        proj = ops.linear(x, w, out_dtype=torch.float32 if x.shape[0] <= ops.GEMV_MAX_ROWS else None)
+        ops.prof_mark("qkv_gemm")
+        q = ops.qkv_post(
+            proj, self.q_norm, self.k_norm, norm.eps if norm else 0.0, norm.weight_offset if norm else 0.0,
+            rotation, batch.row_pos, batch.row_slot, kv.k_pages, kv.v_pages, kv.page_table, kv.page_size,
+            s.num_heads, s.num_kv_heads, s.head_dim, ctx.writes_cache, self.dtype,
+            values_are_keys=self.values_are_keys, ld=cols)
+        ops.prof_mark("norm_rope")
+        attn = ops.attention(q, kv.k_pages, kv.v_pages, kv.page_table, kv.page_size, batch, s.num_heads,
+                             s.num_kv_heads, s.head_dim, s.window, s.scale, keep_first=self.keep_first)
+        if self.output_gate:
+            ops.sigmoid_gate_mul_(attn, proj, gate_col)
+        ops.prof_mark("attn")
         out = ops.linear(attn, self.o, out_dtype=torch.float32)
         ops.prof_mark("o_proj")
         return out

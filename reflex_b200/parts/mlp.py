@@ -112,3 +112,34 @@ class ClampedGLU:
         out = ops.linear(act, self.down, out_dtype=torch.float32)
         ops.prof_mark("ffn_down")
         return out
+
+
+@register_feed_forward("relu2")
+class SquaredReLU:
+    """out = W_down relu(W_up x)^2: no gate, the activation is the square of the
+    rectified product."""
+
+    capturable = True
+
+    def __init__(self, spec: FeedForwardSpec, dtype: torch.dtype, device):
+        self.spec = spec
+        self.dtype = dtype
+        self.device = device
+        self.up = None
+        self.down = None
+
+    @classmethod
+    def tensor_specs(cls, spec: FeedForwardSpec) -> Dict[str, TensorInfo]:
+        H, I = spec.hidden_size, spec.intermediate_size
+        return {"up_proj": TensorInfo((I, H), "matrix"), "down_proj": TensorInfo((H, I), "matrix")}
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.up = tensors["up_proj"].to(device=self.device, dtype=self.dtype).contiguous()
+        self.down = tensors["down_proj"].to(device=self.device, dtype=self.dtype).contiguous()
+
+    def forward(self, x, residual=None):
+        act = ops.linear_relu2(x, self.up)
+        ops.prof_mark("ffn_gate_up")
+        out = ops.linear(act, self.down, out_dtype=torch.float32)
+        ops.prof_mark("ffn_down")
+        return out

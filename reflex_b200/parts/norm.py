@@ -29,7 +29,8 @@ class RMSNorm:
 
     @classmethod
     def tensor_specs(cls, spec: NormSpec) -> Dict[str, TensorInfo]:
-        return {"weight": TensorInfo((spec.size,), "norm")}
+        # a weight that is applied as 1 + w is stored around zero
+        return {"weight": TensorInfo((spec.size,), "norm0" if spec.weight_offset == 1.0 else "norm")}
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         self.weight = tensors["weight"].to(device=self.device, dtype=torch.float32).contiguous()

@@ -43,6 +43,8 @@ class TensorInfo:
     # "norm":   a norm's weight, kept 32-bit, drawn 1 + U(-0.1, 0.1)
     # "bias":   a bias or another small vector, kept 32-bit, drawn U(-0.5, 0.5)
     # "filter": the taps of a short convolution, kept 32-bit, drawn U(-0.6, 0.6)
+    # "norm0":  a norm's weight stored around zero (applied as 1 + w), kept 32-bit, drawn U(-0.1, 0.1)
+    # "coef":   mixing coefficients of several residual streams, kept 32-bit, drawn U(0.2, 0.8)
     role: str
     optional: bool = False
 

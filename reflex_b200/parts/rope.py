@@ -46,3 +46,36 @@ class RotaryNeox:
 
     def rotation(self) -> Rotation:
         return Rotation(self.denominators, self.spec.rotary_dim, "half", 1.0)
+
+
+@register_position("rope_scaled")
+class RotaryScaled(RotaryNeox):
+    """The half-split rotation with wavelength-dependent frequency scaling.
+
+    With f_i = theta^(-2i/rd) and the wavelength l = 2 pi / f_i, and the
+    parameters `factor`, `low`, `high`, `original`: f_i stays where
+    l < original / high; becomes f_i / factor where l > original / low; and in
+    between, with s = (original / l - low) / (high - low), the blend
+    (1 - s) f_i / factor + s f_i.  Only the table of denominators (1 / f_i)
+    differs from the plain encoding."""
+
+    def __init__(self, spec: PositionSpec, dtype: torch.dtype, device):
+        super().__init__(spec, dtype, device)
+        p = dict(spec.params)
+        factor, low, high, original = (float(p[k]) for k in ("factor", "low", "high", "original"))
+        if factor <= 0 or high <= low or original <= 0:
+            raise InvalidInput("rope_scaled: factor and original must be positive and high above low")
+        half = spec.rotary_dim // 2
+        denom = []
+        for i in range(half):
+            f = math.pow(float(spec.theta), -2.0 * i / float(spec.rotary_dim))
+            wave = 2.0 * math.pi / f
+            if wave < original / high:
+                g = f
+            elif wave > original / low:
+                g = f / factor
+            else:
+                s = (original / wave - low) / (high - low)
+                g = (1.0 - s) * f / factor + s * f
+            denom.append(1.0 / g)
+        self.denominators = torch.tensor(denom, dtype=torch.float64).to(torch.float32).to(device)

@@ -76,7 +76,11 @@ def draw_host(key: int, n: int, kind: str, a: float, b: float, first: int = 0) -
 
 
 # every other role: N(0, 0.02); "filter": a short convolution's taps, kept 32-bit like a bias
-ROLE_DRAWS = {"norm": ("uniform", 0.9, 1.1), "bias": ("uniform", -0.5, 0.5), "filter": ("uniform", -0.6, 0.6)}
+# "norm0": a norm weight stored around zero (applied as 1 + w); "coef": the small mixing coefficients of
+# several residual streams
+ROLE_DRAWS = {"norm": ("uniform", 0.9, 1.1), "bias": ("uniform", -0.5, 0.5), "filter": ("uniform", -0.6, 0.6),
+              "norm0": ("uniform", -0.1, 0.1), "coef": ("uniform", 0.2, 0.8)}
+SMALL_ROLES = tuple(ROLE_DRAWS)  # kept 32-bit whatever the compute type
 
 
 def draw(name: str, shape, role: str, seed: int, device="cpu", dtype: torch.dtype = torch.float32) -> torch.Tensor:
@@ -150,6 +154,6 @@ def random_model_on_device(config: Dict[str, Any], seed: int, dtype: torch.dtype
     tensors = {}
     for name, (_where, info) in expected_tensors(spec).items():
         tensors[name] = draw(name, info.shape, info.role, seed, device,
-                             torch.float32 if info.role in ("norm", "bias", "filter") else store)
+                             torch.float32 if info.role in SMALL_ROLES else store)
     model.bind(tensors)
     return model
