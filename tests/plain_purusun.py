@@ -175,13 +175,20 @@ def selective_scan(h: np.ndarray, w: Dict[str, np.ndarray], m: dict) -> np.ndarr
     p = x @ w["x"].T
     dt, B, C = p[:, :R], p[:, R:R + N], p[:, R + N:R + 2 * N]
     dt = softplus(dt @ w["dt"].T + w["dt.b"])          # [T, inner]
-    A = -np.exp(w["A_log"])                            # [inner, N]
-    S = np.zeros((inner, N), dtype=F)
+    y = scan_core(x, dt, -np.exp(w["A_log"]), B, C, w["D"])
+    return (y * silu(z)) @ w["o"].T
+
+
+def scan_core(x, dt, A, B, C, D, S0=None):
+    """x, dt [T, inner]; A [inner, N]; B, C [T, N]; D [inner]: the recurrence
+    S <- exp(dt A) S + dt x B, y = S C + D x, from the state S0 (zeros)."""
+    T, inner = x.shape
+    S = np.zeros(A.shape, dtype=F) if S0 is None else S0.copy()
     y = np.zeros((T, inner), dtype=F)
     for t in range(T):
         S = np.exp(dt[t][:, None] * A) * S + (dt[t] * x[t])[:, None] * B[t][None, :]
-        y[t] = S @ C[t] + w["D"] * x[t]
-    return (y * silu(z)) @ w["o"].T
+        y[t] = S @ C[t] + D * x[t]
+    return y
 
 
 # -------------------------------------------------------------- feed-forward
