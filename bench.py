@@ -299,6 +299,25 @@ def pakarax_config(z):
             "layers": layers}
 
 
+def purusun_config(z):
+    """Purusun at the sizes of `z`: attention layers (a quarter as many key/value
+    heads, half of each head rotated with scaled frequencies, the window of the
+    models beside it with four kept first tokens) and selective-scan layers (twice
+    the width as channels, 16 states, a step-size rank of width / 16, four taps) in
+    turn, every layer with a squared-ReLU feed-forward, four residual streams."""
+    att = {"type": "attention",
+           "mixer": {"heads": z["heads"], "kv_heads": max(1, z["heads"] // 4), "dim": z["dim"], "vdim": z["dim"],
+                     "scale": z["dim"] ** -0.5,
+                     "rot": {"base": 500000.0, "dims": z["dim"] // 2,
+                             "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}},
+                     "mask": {"size": z["window"], "keep_first": 4}}}
+    scan = {"type": "mamba1", "mixer": {"inner": 2 * z["width"], "state": 16, "dt_rank": z["width"] // 16, "conv": 4}}
+    dense = {"kind": "dense", "ff": z["ff"]}
+    layers = [dict((att, scan)[i % 2], mlp=dense) for i in range(z["layers"])]
+    return {"architecture": "Purusun", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5},
+            "streams": 4, "layers": layers}
+
+
 def qwen3_config_like(z):
     cfg = dict(QWEN3_8B)
     cfg.update({"num_hidden_layers": z["layers"], "hidden_size": z["width"], "num_attention_heads": z["heads"],
@@ -324,7 +343,7 @@ def design_comparison(args) -> int:
     T, B, P, steps = PREFILL_TOKENS, args.batch, PROMPT, max(16, min(args.steps, 64))
     mine = args.design
     beside = [("qwen3", qwen3_config_like)] + ([("kegasun", kegasun_config)] if mine == "pakarax" else [])
-    mine_config = {"kegasun": kegasun_config, "pakarax": pakarax_config}[mine]
+    mine_config = {"kegasun": kegasun_config, "pakarax": pakarax_config, "purusun": purusun_config}[mine]
     out = {"metric": f"prefill and decode tokens/s, {mine} beside " + " and ".join(n for n, _ in beside)
                      + " at equal sizes", "unit": "tokens/s",
            "dtype": "bf16", "data": "synthetic: seeded uniform token ids, random-init weights",
@@ -449,7 +468,7 @@ def main() -> int:
                     help="workloads beside the headline: 14b and 32b add their points (default: all)")
     ap.add_argument("--prompt", type=int, default=PROMPT, help="prompt tokens before the decode steps")
     ap.add_argument("--context", type=int, default=CONTEXT, help="cache positions per sequence")
-    ap.add_argument("--design", default="", choices=["", "kegasun", "pakarax"],
+    ap.add_argument("--design", default="", choices=["", "kegasun", "pakarax", "purusun"],
                     help="instead of the headline: this design beside Qwen3 at equal sizes (prefill, decode, phases)")
     ap.add_argument("--sizes", default="w1024,w2048,w4096", help="with --design: which of the sizes " +
                     ", ".join(sorted(DESIGN_SIZES)))
