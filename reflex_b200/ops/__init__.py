@@ -1300,7 +1300,7 @@ def mamba_scan(x: torch.Tensor, dtpre: torch.Tensor, dt_bias: Optional[torch.Ten
         z.shape[1], int(z_off), _chk(A, "A", torch.float32), _chk(D, "D", torch.float32),
         _chk(state, "state", torch.float32), state.stride(0), int(state_off),
         _chk(batch.seq_slot, "seq_slot", torch.int32), _chk(batch.seq_row0, "seq_row0", torch.int32),
-        batch.seq_slot.numel(), out.data_ptr(), dt_code(out_dtype), C, N, _stream())
+        batch.seq_slot.numel(), R, out.data_ptr(), dt_code(out_dtype), C, N, _stream())
     native.check(st, f"mamba_scan (channels={C}, states={N})")
     return out
 

@@ -65,8 +65,8 @@ _SIGNATURES = {
     "rfx_hyper_collapse": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                            c_void_p],
     "rfx_mamba_scan": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int,
-                       c_void_p, c_void_p, c_void_p, c_longlong, c_longlong, c_void_p, c_void_p, c_int, c_void_p,
-                       c_int, c_int, c_int, c_void_p],
+                       c_void_p, c_void_p, c_void_p, c_longlong, c_longlong, c_void_p, c_void_p, c_int, c_int,
+                       c_void_p, c_int, c_int, c_int, c_void_p],
     "rfx_attention_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
                              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
                              c_void_p, c_longlong, c_void_p, c_void_p],

@@ -221,17 +221,21 @@ CUTS = ({0: 37, 1: 9, 2: 1}, {0: 1, 2: 2}, {2: 1}, {0: 2, 2: 14}, {2: 15}, {0: 3
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("C,N,taps", [(48, 8, 3), (24, 1, 1), (50, 5, 5), (256, 64, 4), (16, 130, 2), (36, 16, 4),
                                       (8, 300, 2)])
-def test_filter_silu_and_scan_carried_through_their_state(C, N, taps, out_dtype):
+@pytest.mark.parametrize("gap", [1, 4])
+def test_filter_silu_and_scan_carried_through_their_state(C, N, taps, out_dtype, gap):
     """Three sequences of unequal lengths in steps of unequal sizes, down to one
     and two rows, in slots that are not in order: the filter's last inputs and
     the scan's state go on from what the steps before left; a slot taken again
-    starts from zeros.  Step sizes from nearly zero to several units."""
+    starts from zeros.  Step sizes from nearly zero to several units.  B and C
+    lie `gap` floats into their rows and apart (4: every address a multiple of
+    16 bytes where the sizes allow it; 1: none)."""
     g = torch.Generator().manual_seed(C + N)
+    b_off, c_off, ld_bc = gap, N + 2 * gap, 2 * N + 3 * gap
     lens, slots = {0: 70, 1: 9, 2: 33}, {0: 3, 1: 0, 2: 6}
     ld_z, z_off = 2 * C + 4, C + 4
     xz = {s: torch.randn(n, ld_z, generator=g) for s, n in lens.items()}
     dtpre = {s: torch.randn(n, C, generator=g) * 3 for s, n in lens.items()}
-    bc = {s: torch.randn(n, 2 * N + 3, generator=g) for s, n in lens.items()}
+    bc = {s: torch.randn(n, ld_bc, generator=g) for s, n in lens.items()}
     w, cb = torch.randn(C, taps, generator=g) * 0.6, torch.randn(C, generator=g) * 0.3
     dtb, A = torch.randn(C, generator=g), -torch.exp(torch.randn(C, N, generator=g) * 0.7)
     D = torch.randn(C, generator=g)
@@ -248,7 +252,7 @@ def test_filter_silu_and_scan_carried_through_their_state(C, N, taps, out_dtype)
         u = ops().short_conv(rows, 0, C, None, w.t().contiguous().to(DEV), cb.to(DEV), state if taps > 1 else None, b,
                              activation="silu")
         ops().conv_state_update(rows, 0, C, None, taps, state, b)
-        y = ops().mamba_scan(u, cat(dtpre), dtb.to(DEV), cat(bc), 1, N + 2, rows, z_off, A.to(DEV).contiguous(),
+        y = ops().mamba_scan(u, cat(dtpre), dtb.to(DEV), cat(bc), b_off, c_off, rows, z_off, A.to(DEV).contiguous(),
                              D.to(DEV), state, (taps - 1) * C, b, out_dtype)
         for j, s in enumerate(ids):
             got[s].append(y[b.row0[j]:b.row0[j + 1]].float().cpu())
@@ -257,7 +261,7 @@ def test_filter_silu_and_scan_carried_through_their_state(C, N, taps, out_dtype)
     def ref(s):
         x = pp.silu(pp.causal_conv(xz[s][:, :C].double().numpy(), w.double().numpy(), cb.double().numpy()))
         dt = pp.softplus(dtpre[s].double().numpy() + dtb.double().numpy())
-        B, Cm = bc[s][:, 1:1 + N].double().numpy(), bc[s][:, N + 2:2 * N + 2].double().numpy()
+        B, Cm = bc[s][:, b_off:b_off + N].double().numpy(), bc[s][:, c_off:c_off + N].double().numpy()
         y = pp.scan_core(x, dt, A.double().numpy(), B, Cm, D.double().numpy())
         return y * pp.silu(xz[s][:, z_off:z_off + C].double().numpy())
 
@@ -272,7 +276,7 @@ def test_filter_silu_and_scan_carried_through_their_state(C, N, taps, out_dtype)
     rows = xz[1].to(DEV)
     u = ops().short_conv(rows, 0, C, None, w.t().contiguous().to(DEV), cb.to(DEV), state if taps > 1 else None, b,
                          activation="silu")
-    y = ops().mamba_scan(u, dtpre[1].to(DEV), dtb.to(DEV), bc[1].to(DEV), 1, N + 2, rows, z_off,
+    y = ops().mamba_scan(u, dtpre[1].to(DEV), dtb.to(DEV), bc[1].to(DEV), b_off, c_off, rows, z_off,
                          A.to(DEV).contiguous(), D.to(DEV), state, (taps - 1) * C, b, out_dtype)
     assert relerr(y, ref(1)) < tol
 
