@@ -19,15 +19,24 @@
 // in order; the next row's operands are loaded while this row's chain runs.
 // That form serves steps of a row or two a sequence (decoding).
 //
-// Prompts take the tiled form: a block walks its sequence in tiles of TT rows.
-// The tile's operands (its channels' x, dt and z, the rows' B and C) arrive in
-// shared memory by asynchronous copies while the tile before is computed, so a
-// step of the recurrence waits for no load.  Per tile: (A) every thread turns
+// Prompts take the tiled, segmented form.  A lane holds up to 16 states of a
+// channel (one lane a channel up to 16 states: no shuffles, sixteen independent
+// chains a row), and since that leaves few threads, a sequence's rows are cut
+// into G segments that run side by side.  The recurrence is linear in S, so
+//   (1) every segment but the last folds its rows from S = 0 into S_local and
+//       the sum of its step sizes (the segment's decay is exp(A * that sum)),
+//   (2) a small kernel carries the sequence's state through the segments,
+//       S_begin[g + 1] = exp(A * sum_dt[g]) * S_begin[g] + S_local[g],
+//   (3) every segment runs again from its S_begin and writes its rows; the last
+//       one leaves the sequence's state.
+// With G = 1 only (3) runs, from the state.  A block walks its segment in tiles
+// of TT rows whose operands (its channels' x, dt and z, the rows' B and C) arrive
+// in shared memory by asynchronous copies while the tile before is computed, so
+// a step of the recurrence waits for no load.  Per tile: (A) every thread turns
 // some of the tile's dt into softplus(dt + bias) and z into silu(z), each once a
-// channel and not once a lane; (B) the recurrence, four rows an iteration so
-// that the exponentials and the lanes' shuffles of four rows overlap and only
-// the multiply-add on S is a chain; (C) the tile's results leave in row order.
-// Both forms do the same 32-bit arithmetic in the same order on S.
+// channel; (B) the recurrence; (C) the tile's results leave in row order.
+// The decay of a step is 2^(dt * A * log2 e) in every form, A * log2 e made when
+// the block starts.
 #include "common.cuh"
 
 namespace {
@@ -36,7 +45,15 @@ using namespace rfx;
 
 constexpr int THREADS = 128;
 
+constexpr float LOG2E = 1.4426950408889634f;
+
 __device__ __forceinline__ float softplus_f(float v) { return fmaxf(v, 0.0f) + log1pf(expf(-fabsf(v))); }
+// 2^v for v <= 0 (a decay): the hardware's base-2 exponential, results below 2^-126 are zero
+__device__ __forceinline__ float decay2(float v) {
+    float r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
+    return r;
+}
 
 template <typename TO, int NPL>
 __global__ void __launch_bounds__(THREADS)
@@ -57,7 +74,7 @@ mamba_scan_kernel(const float* __restrict__ x, const float* __restrict__ dtpre, 
 #pragma unroll
     for (int i = 0; i < NPL; ++i) {
         const int n = sub + i * lpc;
-        a[i] = n < N ? A[(size_t)cc * N + n] : 0.0f;
+        a[i] = n < N ? A[(size_t)cc * N + n] * LOG2E : 0.0f;
     }
     const float bias = dt_bias ? dt_bias[cc] : 0.0f;
     const float d_skip = Dw ? Dw[cc] : 0.0f;
@@ -101,7 +118,7 @@ mamba_scan_kernel(const float* __restrict__ x, const float* __restrict__ dtpre, 
         float y = 0.0f;
 #pragma unroll
         for (int i = 0; i < NPL; ++i) {
-            S[i] = fmaf(expf(dt * a[i]), S[i], dx * Bt[i]);
+            S[i] = fmaf(decay2(dt * a[i]), S[i], dx * Bt[i]);
             y = fmaf(S[i], Ct[i], y);
         }
         for (int o = lpc >> 1; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
@@ -121,7 +138,7 @@ mamba_scan_kernel(const float* __restrict__ x, const float* __restrict__ dtpre, 
 }
 
 
-// ---------------------------------------------------------------- tiled form
+// ------------------------------------------------------- tiled, segmented form
 __device__ __forceinline__ void copy_async16(float* dst, const float* src) {
     const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
@@ -135,220 +152,308 @@ template <int K> __device__ __forceinline__ void copy_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(K) : "memory");
 }
 
+// segment g of G of a sequence of `rows` rows: [begin, begin + count)
+__device__ __forceinline__ void segment_of(int rows, int G, int g, int& begin, int& count) {
+    const int L = (rows + G - 1) / G;
+    begin = min(rows, g * L);
+    count = min(rows, begin + L) - begin;
+}
+
+// How the threads of a block share its work, the same for all three kernels.
+struct ScanPlan {
+    int lpc;       // lanes a channel (a power of two), lane j holds states j * NPL ...
+    int lp_shift;  // log2(lpc)
+    int ch_shift;  // log2(channels of a block) = log2(THREADS / lpc)
+    int TT;        // rows a tile
+    int G;         // segments a sequence
+};
+
 // V floats a copy: 4 where every address involved is a multiple of 16 bytes, else 1.
-template <typename TO, int NPL, int V>
+// FOLD: step (1), no output; else step (3).
+template <typename TO, int NPL, int V, bool FOLD>
 __global__ void __launch_bounds__(THREADS)
 mamba_scan_tiled_kernel(const float* __restrict__ x, const float* __restrict__ dtpre,
                         const float* __restrict__ dt_bias, const float* __restrict__ bc, int ld_bc, int b_off,
                         int c_off, const float* __restrict__ zsrc, int ld_z, int z_off,
                         const float* __restrict__ A, const float* __restrict__ Dw, float* __restrict__ state,
                         size_t slot_stride, size_t state_off, const int* __restrict__ seq_slot,
-                        const int* __restrict__ seq_row0, TO* __restrict__ out, int channels, int N, int lpc,
-                        int TT) {
+                        const int* __restrict__ seq_row0, TO* __restrict__ out, int channels, int N,
+                        ScanPlan plan, float* __restrict__ seg_local, float* __restrict__ seg_dt,
+                        const float* __restrict__ seg_begin) {
     extern __shared__ float4 tiles4[];
     float* tiles = reinterpret_cast<float*>(tiles4);
     pdl_launch_dependents();
-    const int CH = THREADS / lpc;                            // channels of a block
+    const int G = plan.G, g = blockIdx.z;
+    if (FOLD && g == G - 1) return;  // the last segment's fold is nobody's input
+    const int TT = plan.TT;
+    const int CH = 1 << plan.ch_shift;
     const int stage_floats = TT * (3 * CH + 2 * N);
     const int s = blockIdx.x;
     const int c0 = blockIdx.y * CH;
-    const int lc = threadIdx.x / lpc, sub = threadIdx.x % lpc;
+    const int lc = threadIdx.x >> plan.lp_shift, sub = threadIdx.x & (plan.lpc - 1);
     const int c = c0 + lc;
     const bool live = c < channels;
     const int cc = live ? c : channels - 1;
-    float a[NPL];
+    const int n0 = sub * NPL;
+    float a2[NPL];
 #pragma unroll
-    for (int i = 0; i < NPL; ++i) {
-        const int n = sub + i * lpc;
-        a[i] = n < N ? A[(size_t)cc * N + n] : 0.0f;
-    }
-    const float d_skip = Dw ? Dw[cc] : 0.0f;
+    for (int i = 0; i < NPL; ++i) a2[i] = n0 + i < N ? A[(size_t)cc * N + n0 + i] * LOG2E : 0.0f;
+    const float d_skip = (!FOLD && Dw) ? Dw[cc] : 0.0f;
     pdl_wait();
     const int row0 = seq_row0[s], rows = seq_row0[s + 1] - row0;
+    int seg0, count;
+    segment_of(rows, G, g, seg0, count);
+    const size_t seg_cell = ((size_t)s * G + g) * channels + cc;  // this channel's place in the segments' arrays
     float* st_c = state + (size_t)seq_slot[s] * slot_stride + state_off + (size_t)cc * N;
     float S[NPL];
 #pragma unroll
     for (int i = 0; i < NPL; ++i) {
-        const int n = sub + i * lpc;
-        S[i] = n < N ? st_c[n] : 0.0f;
+        if (FOLD || n0 + i >= N) S[i] = 0.0f;
+        else S[i] = G == 1 ? st_c[n0 + i] : seg_begin[seg_cell * N + n0 + i];
     }
-    const int ntiles = (rows + TT - 1) / TT;
-    // a tile's operands into stage `g`; rows past the sequence's end and channels past
-    // the last one are zeros (a zero step leaves S as it is)
-    auto load = [&](int k, int g) {
-        float* xs = tiles + (size_t)g * stage_floats;
+    float sum_dt = 0.0f;
+    const int ntiles = (count + TT - 1) / TT;
+    auto load = [&](int k, int st) {
+        float* xs = tiles + (size_t)st * stage_floats;
         float* ds = xs + TT * CH;
         float* zs = ds + TT * CH;
         float* bs = zs + TT * CH;
         float* cs = bs + TT * N;
-        const int t_begin = k * TT;
-        const int valid = min(TT, rows - t_begin);
-        const int padded = min(TT, (valid + 3) & ~3);
-        for (int i = threadIdx.x * V; i < padded * CH; i += THREADS * V) {
-            const int t = i / CH, l = i % CH;
+        const int t_begin = seg0 + k * TT;
+        const int valid = min(TT, seg0 + count - t_begin);
+        for (int i = threadIdx.x * V; i < valid * CH; i += THREADS * V) {
+            const int t = i >> plan.ch_shift, l = i & (CH - 1);
+            if (c0 + l >= channels) continue;
             const size_t r = (size_t)(row0 + t_begin + t);
-            if (t < valid && c0 + l < channels) {
-                if (V == 4) {
-                    copy_async16(xs + i, x + r * channels + c0 + l);
-                    copy_async16(ds + i, dtpre + r * channels + c0 + l);
-                    copy_async16(zs + i, zsrc + r * ld_z + z_off + c0 + l);
-                } else {
-                    copy_async4(xs + i, x + r * channels + c0 + l);
-                    copy_async4(ds + i, dtpre + r * channels + c0 + l);
-                    copy_async4(zs + i, zsrc + r * ld_z + z_off + c0 + l);
-                }
+            if (V == 4) {
+                copy_async16(xs + i, x + r * channels + c0 + l);
+                copy_async16(ds + i, dtpre + r * channels + c0 + l);
+                if (!FOLD) copy_async16(zs + i, zsrc + r * ld_z + z_off + c0 + l);
             } else {
-#pragma unroll
-                for (int v = 0; v < V; ++v) xs[i + v] = ds[i + v] = zs[i + v] = 0.0f;
+                copy_async4(xs + i, x + r * channels + c0 + l);
+                copy_async4(ds + i, dtpre + r * channels + c0 + l);
+                if (!FOLD) copy_async4(zs + i, zsrc + r * ld_z + z_off + c0 + l);
             }
         }
-        for (int i = threadIdx.x * V; i < padded * N; i += THREADS * V) {
-            const int t = i / N, n = i % N;
+        for (int i = threadIdx.x * V; i < valid * N; i += THREADS * V) {
+            const int t = i / N, n = i - t * N;
             const float* brow = bc + (size_t)(row0 + t_begin + t) * ld_bc;
-            if (t < valid) {
-                if (V == 4) {
-                    copy_async16(bs + i, brow + b_off + n);
-                    copy_async16(cs + i, brow + c_off + n);
-                } else {
-                    copy_async4(bs + i, brow + b_off + n);
-                    copy_async4(cs + i, brow + c_off + n);
-                }
+            if (V == 4) {
+                copy_async16(bs + i, brow + b_off + n);
+                if (!FOLD) copy_async16(cs + i, brow + c_off + n);
             } else {
-#pragma unroll
-                for (int v = 0; v < V; ++v) bs[i + v] = cs[i + v] = 0.0f;
+                copy_async4(bs + i, brow + b_off + n);
+                if (!FOLD) copy_async4(cs + i, brow + c_off + n);
             }
         }
     };
     if (ntiles > 0) load(0, 0);
     copy_commit();
+    const bool by4 = NPL % 4 == 0 && N % 4 == 0;
     for (int k = 0; k < ntiles; ++k) {
-        const int g = k & 1;
-        if (k + 1 < ntiles) load(k + 1, g ^ 1);
+        const int st = k & 1;
+        if (k + 1 < ntiles) load(k + 1, st ^ 1);
         copy_commit();
         copy_wait<1>();
         __syncthreads();
-        float* xs = tiles + (size_t)g * stage_floats;
-        float* ds = xs + TT * CH;
-        float* zs = ds + TT * CH;
-        const float* bs = zs + TT * CH;
-        const float* cs = bs + TT * N;
-        const int t_begin = k * TT;
-        const int valid = min(TT, rows - t_begin);
-        const int padded = min(TT, (valid + 3) & ~3);
+        float* __restrict__ xs = tiles + (size_t)st * stage_floats;
+        float* __restrict__ ds = xs + TT * CH;
+        float* __restrict__ zs = ds + TT * CH;
+        const float* __restrict__ bs = zs + TT * CH;
+        const float* __restrict__ cs = bs + TT * N;
+        const int t_begin = seg0 + k * TT;
+        const int valid = min(TT, seg0 + count - t_begin);
         // (A) step sizes and gates, once a channel
-        for (int i = threadIdx.x; i < padded * CH; i += THREADS) {
-            const int t = i / CH, l = i % CH;
-            const int ch = min(c0 + l, channels - 1);
-            const float zt = zs[i];
-            ds[i] = t < valid ? softplus_f(ds[i] + (dt_bias ? dt_bias[ch] : 0.0f)) : 0.0f;
-            zs[i] = zt / (1.0f + expf(-zt));
+        for (int i = threadIdx.x; i < valid * CH; i += THREADS) {
+            const int l = i & (CH - 1);
+            if (c0 + l >= channels) continue;
+            ds[i] = softplus_f(ds[i] + (dt_bias ? dt_bias[c0 + l] : 0.0f));
+            if (!FOLD) {
+                const float zt = zs[i];
+                zs[i] = zt / (1.0f + expf(-zt));
+            }
         }
         __syncthreads();
-        // (B) the recurrence, four rows an iteration
-        for (int t0 = 0; t0 < padded; t0 += 4) {
-            float y[4], xt[4];
+        // (B) the recurrence: per row NPL independent multiply-adds on S
+#pragma unroll 2
+        for (int t = 0; t < valid; ++t) {
+            const float dt = ds[t * CH + lc];
+            const float xt = xs[t * CH + lc];
+            const float dx = dt * xt;
+            float Bt[NPL], Ct[NPL];
+            if (by4) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int t = t0 + j;
-                const float dt = ds[t * CH + lc];
-                xt[j] = xs[t * CH + lc];
-                const float dx = dt * xt[j];
-                float acc = 0.0f;
+                for (int i = 0; i < NPL; i += 4) {
+                    float4 b4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f), c4 = b4;
+                    if (n0 + i < N) {
+                        b4 = *reinterpret_cast<const float4*>(bs + t * N + n0 + i);
+                        if (!FOLD) c4 = *reinterpret_cast<const float4*>(cs + t * N + n0 + i);
+                    }
+                    Bt[i] = b4.x; Bt[(i + 1) % NPL] = b4.y; Bt[(i + 2) % NPL] = b4.z; Bt[(i + 3) % NPL] = b4.w;
+                    Ct[i] = c4.x; Ct[(i + 1) % NPL] = c4.y; Ct[(i + 2) % NPL] = c4.z; Ct[(i + 3) % NPL] = c4.w;
+                }
+            } else {
 #pragma unroll
                 for (int i = 0; i < NPL; ++i) {
-                    const int n = sub + i * lpc;
-                    const float Bt = n < N ? bs[t * N + n] : 0.0f;
-                    const float Ct = n < N ? cs[t * N + n] : 0.0f;
-                    S[i] = fmaf(expf(dt * a[i]), S[i], dx * Bt);
-                    acc = fmaf(S[i], Ct, acc);
+                    Bt[i] = n0 + i < N ? bs[t * N + n0 + i] : 0.0f;
+                    Ct[i] = (!FOLD && n0 + i < N) ? cs[t * N + n0 + i] : 0.0f;
                 }
-                y[j] = acc;
             }
-            for (int o = lpc >> 1; o > 0; o >>= 1) {
+            float acc = 0.0f;
 #pragma unroll
-                for (int j = 0; j < 4; ++j) y[j] += __shfl_xor_sync(0xffffffffu, y[j], o);
+            for (int i = 0; i < NPL; ++i) {
+                S[i] = fmaf(decay2(dt * a2[i]), S[i], dx * Bt[i]);
+                if (!FOLD) acc = fmaf(S[i], Ct[i], acc);
             }
-            if (sub == 0) {
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int i = (t0 + j) * CH + lc;
-                    zs[i] = fmaf(d_skip, xt[j], y[j]) * zs[i];
-                }
+            if (FOLD) {
+                sum_dt += dt;
+            } else {
+                for (int o = plan.lpc >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+                if (sub == 0) zs[t * CH + lc] = fmaf(d_skip, xt, acc) * zs[t * CH + lc];
             }
         }
         __syncthreads();
         // (C) the tile's results
-        for (int i = threadIdx.x; i < valid * CH; i += THREADS) {
-            const int t = i / CH, l = i % CH;
-            if (c0 + l < channels) rfx::st<TO>(out, (size_t)(row0 + t_begin + t) * channels + c0 + l, zs[i]);
+        if (!FOLD) {
+            for (int i = threadIdx.x; i < valid * CH; i += THREADS) {
+                const int t = i >> plan.ch_shift, l = i & (CH - 1);
+                if (c0 + l < channels) rfx::st<TO>(out, (size_t)(row0 + t_begin + t) * channels + c0 + l, zs[i]);
+            }
+            __syncthreads();
         }
-        __syncthreads();
     }
     copy_wait<0>();
-    if (live) {
+    if (!live) return;
+    if (FOLD) {
 #pragma unroll
-        for (int i = 0; i < NPL; ++i) {
-            const int n = sub + i * lpc;
-            if (n < N) st_c[n] = S[i];
-        }
+        for (int i = 0; i < NPL; ++i)
+            if (n0 + i < N) seg_local[seg_cell * N + n0 + i] = S[i];
+        if (sub == 0) seg_dt[seg_cell] = sum_dt;
+    } else if (g == G - 1) {
+#pragma unroll
+        for (int i = 0; i < NPL; ++i)
+            if (n0 + i < N) st_c[n0 + i] = S[i];
+    }
+}
+
+// step (2): a thread a (sequence, channel, state) carries S through the segments
+__global__ void __launch_bounds__(256)
+mamba_scan_carry_kernel(const float* __restrict__ A, const float* __restrict__ state, size_t slot_stride,
+                        size_t state_off, const int* __restrict__ seq_slot, const float* __restrict__ seg_local,
+                        const float* __restrict__ seg_dt, float* __restrict__ seg_begin, int channels, int N,
+                        int G) {
+    pdl_launch_dependents();
+    const int s = blockIdx.x;
+    const size_t e = (size_t)blockIdx.y * blockDim.x + threadIdx.x;
+    const size_t per = (size_t)channels * N;
+    if (e >= per) return;
+    const int c = (int)(e / N);
+    const float a2 = A[e] * LOG2E;
+    pdl_wait();
+    float S = state[(size_t)seq_slot[s] * slot_stride + state_off + e];
+#pragma unroll 4
+    for (int g = 0; g < G; ++g) {
+        const size_t cell = (size_t)s * G + g;
+        seg_begin[cell * per + e] = S;
+        if (g < G - 1) S = fmaf(decay2(a2 * seg_dt[cell * channels + c]), S, seg_local[cell * per + e]);
     }
 }
 
 }  // namespace
 
+// how a step of R rows in S sequences is laid out; G = 0: the row-by-row form
+static ScanPlan scan_plan(int S, int R, int channels, int N) {
+    ScanPlan p{};
+    if (R < 4 * S) return p;
+    p.lpc = 1;
+    while (p.lpc < 32 && p.lpc * 16 < N) p.lpc <<= 1;
+    for (int v = p.lpc; v > 1; v >>= 1) ++p.lp_shift;
+    for (int v = THREADS / p.lpc; v > 1; v >>= 1) ++p.ch_shift;
+    const int CH = THREADS / p.lpc;
+    p.TT = 16;
+    while (p.TT > 4 && (size_t)2 * p.TT * (3 * CH + 2 * N) * sizeof(float) > 72 * 1024) p.TT >>= 1;
+    // segments: enough for about four warps a scheduler, of 32 rows and more each
+    const long long warps = (long long)S * ((channels + CH - 1) / CH) * (THREADS / 32);
+    long long G = (rfx::sm_count() * 16 + warps - 1) / warps;
+    const long long longest = (R / S) / 32;
+    if (G > longest) G = longest;
+    if (G > 64) G = 64;
+    if (G < 1) G = 1;
+    p.G = (int)G;
+    return p;
+}
+
+// floats of scratch that rfx_mamba_scan wants for this step (0: none)
+extern "C" long long rfx_mamba_scan_scratch(int S, int R, int channels, int N) {
+    if (S <= 0 || channels <= 0 || N < 1 || N > 512) return 0;
+    const ScanPlan p = scan_plan(S, R, channels, N);
+    if (p.G <= 1) return 0;
+    return (long long)S * p.G * channels * (2LL * N + 1);
+}
+
 // x, dtpre: float32 [R][channels].  `bc`: float32 rows of `ld_bc` floats that hold
 // B at column `b_off` and C at `c_off` (N each).  `zsrc`: float32 rows of `ld_z`
 // floats with z at column `z_off`.  A: [channels][N] (negative).  `state`:
 // [slots][slot_stride] floats, this mixer's S at `state_off`.  R rows in all, of S
-// sequences: steps of four rows a sequence and more take the tiled form.
+// sequences: steps of four rows a sequence and more take the tiled form, which
+// wants `scratch` (rfx_mamba_scan_scratch floats) when it cuts sequences into segments.
 extern "C" int rfx_mamba_scan(const float* x, const float* dtpre, const float* dt_bias, const float* bc,
                               int ld_bc, int b_off, int c_off, const float* zsrc, int ld_z, int z_off,
                               const float* A, const float* Dw, float* state, long long slot_stride,
                               long long state_off, const int* seq_slot, const int* seq_row0, int S, int R,
-                              void* out, int out_dt, int channels, int N, void* stream) {
+                              void* out, int out_dt, int channels, int N, float* scratch, void* stream) {
     if (S <= 0 || channels <= 0) return 0;
     if (N < 1 || N > 512) return RFX_ERR_UNSUPPORTED;
+    if (out_dt != RFX_DT_F32 && out_dt != RFX_DT_BF16) return RFX_ERR_BAD_ARG;
     cudaStream_t st = (cudaStream_t)stream;
-    if (R >= 4 * S) {
-        // prompts: the tiled form, two states a lane where the channel's lanes reach
-        int lpc = 1;
-        while (lpc < 32 && lpc * 2 < N) lpc <<= 1;
+    const ScanPlan plan = scan_plan(S, R, channels, N);
+    if (plan.G >= 1) {
+        const int lpc = plan.lpc, CH = THREADS / lpc, TT = plan.TT, G = plan.G;
         const int npl = (N + lpc - 1) / lpc;
-        const int CH = THREADS / lpc;
-        int TT = 32;
-        while (TT > 4 && (size_t)2 * TT * (3 * CH + 2 * N) * sizeof(float) > 160 * 1024) TT >>= 1;
         const size_t smem = (size_t)2 * TT * (3 * CH + 2 * N) * sizeof(float);
-        const dim3 grid(S, (channels + CH - 1) / CH);
+        const dim3 grid(S, (channels + CH - 1) / CH, G);
         if (grid.y > 65535 || smem > 200 * 1024) return RFX_ERR_UNSUPPORTED;
+        if (G > 1 && !scratch) return RFX_ERR_BAD_ARG;
+        const size_t cells = (size_t)S * G * channels;
+        float* seg_local = scratch;
+        float* seg_begin = scratch ? scratch + cells * N : nullptr;
+        float* seg_dt = scratch ? scratch + 2 * cells * N : nullptr;
         auto aligned = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
-        const bool wide = CH % 4 == 0 && channels % 4 == 0 && N % 4 == 0 && ld_bc % 4 == 0 && b_off % 4 == 0 &&
-                          c_off % 4 == 0 && ld_z % 4 == 0 && z_off % 4 == 0 && aligned(x) && aligned(dtpre) &&
-                          aligned(bc) && aligned(zsrc);
-#define RFX_TILED(TO, P, V)                                                                                    \
-    do {                                                                                                       \
-        if (smem > 48 * 1024)                                                                                  \
-            cudaFuncSetAttribute(mamba_scan_tiled_kernel<TO, P, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                                 (int)smem);                                                                   \
-        RFX_LAUNCH((mamba_scan_tiled_kernel<TO, P, V>), grid, THREADS, smem, st, x, dtpre, dt_bias, bc, ld_bc,  \
-                   b_off, c_off, zsrc, ld_z, z_off, A, Dw, state, (size_t)slot_stride, (size_t)state_off,      \
-                   seq_slot, seq_row0, (TO*)out, channels, N, lpc, TT);                                        \
+        const bool wide = channels % 4 == 0 && N % 4 == 0 && ld_bc % 4 == 0 && b_off % 4 == 0 && c_off % 4 == 0 &&
+                          ld_z % 4 == 0 && z_off % 4 == 0 && aligned(x) && aligned(dtpre) && aligned(bc) &&
+                          aligned(zsrc);
+#define RFX_TILED(TO, P, V, FOLD)                                                                                 \
+    do {                                                                                                          \
+        if (smem > 48 * 1024)                                                                                     \
+            cudaFuncSetAttribute(mamba_scan_tiled_kernel<TO, P, V, FOLD>,                                         \
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                         \
+        RFX_LAUNCH((mamba_scan_tiled_kernel<TO, P, V, FOLD>), grid, THREADS, smem, st, x, dtpre, dt_bias, bc,     \
+                   ld_bc, b_off, c_off, zsrc, ld_z, z_off, A, Dw, state, (size_t)slot_stride, (size_t)state_off,  \
+                   seq_slot, seq_row0, (TO*)out, channels, N, plan, seg_local, seg_dt, (const float*)seg_begin);  \
     } while (0)
-#define RFX_TILED_N(TO, V)                       \
-    do {                                         \
-        if (npl <= 1) RFX_TILED(TO, 1, V);       \
-        else if (npl <= 2) RFX_TILED(TO, 2, V);  \
-        else if (npl <= 4) RFX_TILED(TO, 4, V);  \
-        else if (npl <= 8) RFX_TILED(TO, 8, V);  \
-        else RFX_TILED(TO, 16, V);               \
+#define RFX_TILED_N(TO, V, FOLD)                       \
+    do {                                               \
+        if (npl <= 1) RFX_TILED(TO, 1, V, FOLD);       \
+        else if (npl <= 2) RFX_TILED(TO, 2, V, FOLD);  \
+        else if (npl <= 4) RFX_TILED(TO, 4, V, FOLD);  \
+        else if (npl <= 8) RFX_TILED(TO, 8, V, FOLD);  \
+        else RFX_TILED(TO, 16, V, FOLD);               \
     } while (0)
+        if (G > 1) {
+            // the fold writes no rows: one output type serves
+            if (wide) RFX_TILED_N(float, 4, true);
+            else RFX_TILED_N(float, 1, true);
+            const size_t per = (size_t)channels * N;
+            RFX_LAUNCH(mamba_scan_carry_kernel, dim3(S, (unsigned)((per + 255) / 256)), 256, 0, st, A,
+                       (const float*)state, (size_t)slot_stride, (size_t)state_off, seq_slot,
+                       (const float*)seg_local, (const float*)seg_dt, seg_begin, channels, N, G);
+        }
         if (out_dt == RFX_DT_F32) {
-            if (wide) RFX_TILED_N(float, 4);
-            else RFX_TILED_N(float, 1);
-        } else if (out_dt == RFX_DT_BF16) {
-            if (wide) RFX_TILED_N(__nv_bfloat16, 4);
-            else RFX_TILED_N(__nv_bfloat16, 1);
+            if (wide) RFX_TILED_N(float, 4, false);
+            else RFX_TILED_N(float, 1, false);
         } else {
-            return RFX_ERR_BAD_ARG;
+            if (wide) RFX_TILED_N(__nv_bfloat16, 4, false);
+            else RFX_TILED_N(__nv_bfloat16, 1, false);
         }
 #undef RFX_TILED_N
 #undef RFX_TILED
@@ -373,8 +478,7 @@ extern "C" int rfx_mamba_scan(const float* x, const float* dtpre, const float* d
         else RFX_SCAN(TO, 16);               \
     } while (0)
     if (out_dt == RFX_DT_F32) RFX_SCAN_N(float);
-    else if (out_dt == RFX_DT_BF16) RFX_SCAN_N(__nv_bfloat16);
-    else return RFX_ERR_BAD_ARG;
+    else RFX_SCAN_N(__nv_bfloat16);
 #undef RFX_SCAN_N
 #undef RFX_SCAN
     return 0;

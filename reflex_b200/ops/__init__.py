@@ -1294,13 +1294,18 @@ def mamba_scan(x: torch.Tensor, dtpre: torch.Tensor, dt_bias: Optional[torch.Ten
     if max(b_off, c_off) + N > bc.shape[1] or z_off + C > z.shape[1]:
         raise InvalidInput("mamba_scan: B, C or z do not fit into their rows")
     out = _new((R, C), out_dtype, x.device)
+    n_seq = batch.seq_slot.numel()
+    # a prompt's rows are cut into segments that run side by side: their folded states
+    want = int(native.lib().rfx_mamba_scan_scratch(n_seq, R, C, N))
+    scratch = _new((want,), torch.float32, x.device) if want > 0 else None
     st = native.lib().rfx_mamba_scan(
         _chk(x, "x", torch.float32), _chk(dtpre, "dtpre", torch.float32), _chk(dt_bias, "dt_bias", torch.float32),
         _chk(bc, "bc", torch.float32), bc.shape[1], int(b_off), int(c_off), _chk(z, "z", torch.float32),
         z.shape[1], int(z_off), _chk(A, "A", torch.float32), _chk(D, "D", torch.float32),
         _chk(state, "state", torch.float32), state.stride(0), int(state_off),
         _chk(batch.seq_slot, "seq_slot", torch.int32), _chk(batch.seq_row0, "seq_row0", torch.int32),
-        batch.seq_slot.numel(), R, out.data_ptr(), dt_code(out_dtype), C, N, _stream())
+        n_seq, R, out.data_ptr(), dt_code(out_dtype), C, N, scratch.data_ptr() if scratch is not None else None,
+        _stream())
     native.check(st, f"mamba_scan (channels={C}, states={N})")
     return out
 

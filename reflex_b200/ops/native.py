@@ -66,7 +66,7 @@ _SIGNATURES = {
                            c_void_p],
     "rfx_mamba_scan": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int,
                        c_void_p, c_void_p, c_void_p, c_longlong, c_longlong, c_void_p, c_void_p, c_int, c_int,
-                       c_void_p, c_int, c_int, c_int, c_void_p],
+                       c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
     "rfx_attention_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
                              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
                              c_void_p, c_longlong, c_void_p, c_void_p],
@@ -155,6 +155,8 @@ def lib() -> ctypes.CDLL:
         handle.rfx_gemm_bf16_tc_max_parts.restype = c_int
         handle.rfx_mlstm_state_floats.argtypes = [c_int, c_int]
         handle.rfx_mlstm_state_floats.restype = c_int
+        handle.rfx_mamba_scan_scratch.argtypes = [c_int, c_int, c_int, c_int]
+        handle.rfx_mamba_scan_scratch.restype = c_longlong
         handle.rfx_sm_count.argtypes = []
         handle.rfx_sm_count.restype = c_int
         handle.rfx_sample_work_bytes.argtypes = [c_int, c_int]

@@ -215,7 +215,9 @@ def test_sigmoid_gate_from_columns_of_a_wider_row_and_squared_relu(a_dtype, z_dt
             (1e-6 if a_dtype == torch.float32 else 8e-3)
 
 
-CUTS = ({0: 37, 1: 9, 2: 1}, {0: 1, 2: 2}, {2: 1}, {0: 2, 2: 14}, {2: 15}, {0: 30})  # rows per sequence and step
+# rows per sequence and step; the first step is long enough for the scan to cut its sequences
+# into segments (also the one of nine rows), the last but one for one sequence in three
+CUTS = ({0: 197, 1: 9, 2: 81}, {0: 1, 2: 2}, {2: 1}, {0: 2, 2: 14}, {2: 115}, {0: 30})
 
 
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
@@ -231,7 +233,7 @@ def test_filter_silu_and_scan_carried_through_their_state(C, N, taps, out_dtype,
     16 bytes where the sizes allow it; 1: none)."""
     g = torch.Generator().manual_seed(C + N)
     b_off, c_off, ld_bc = gap, N + 2 * gap, 2 * N + 3 * gap
-    lens, slots = {0: 70, 1: 9, 2: 33}, {0: 3, 1: 0, 2: 6}
+    lens, slots = {0: 230, 1: 9, 2: 213}, {0: 3, 1: 0, 2: 6}
     ld_z, z_off = 2 * C + 4, C + 4
     xz = {s: torch.randn(n, ld_z, generator=g) for s, n in lens.items()}
     dtpre = {s: torch.randn(n, C, generator=g) * 3 for s, n in lens.items()}
