@@ -249,6 +249,9 @@ mamba_scan_tiled_kernel(const float* __restrict__ x, const float* __restrict__ d
     };
     if (ntiles > 0) load(0, 0);
     copy_commit();
+    const int mine = c0 + (threadIdx.x & (CH - 1));  // the channel of this thread's share of (A)
+    const bool mine_live = mine < channels;
+    const float mine_bias = (dt_bias && mine_live) ? dt_bias[mine] : 0.0f;
     const bool by4 = NPL % 4 == 0 && N % 4 == 0;
     for (int k = 0; k < ntiles; ++k) {
         const int st = k & 1;
@@ -264,10 +267,10 @@ mamba_scan_tiled_kernel(const float* __restrict__ x, const float* __restrict__ d
         const int t_begin = seg0 + k * TT;
         const int valid = min(TT, seg0 + count - t_begin);
         // (A) step sizes and gates, once a channel
+        // (a thread meets the same channel every time: the block's threads are a multiple of CH)
         for (int i = threadIdx.x; i < valid * CH; i += THREADS) {
-            const int l = i & (CH - 1);
-            if (c0 + l >= channels) continue;
-            ds[i] = softplus_f(ds[i] + (dt_bias ? dt_bias[c0 + l] : 0.0f));
+            if (!mine_live) break;
+            ds[i] = softplus_f(ds[i] + mine_bias);
             if (!FOLD) {
                 const float zt = zs[i];
                 zs[i] = zt / (1.0f + expf(-zt));
@@ -351,11 +354,24 @@ mamba_scan_carry_kernel(const float* __restrict__ A, const float* __restrict__ s
     const float a2 = A[e] * LOG2E;
     pdl_wait();
     float S = state[(size_t)seq_slot[s] * slot_stride + state_off + e];
-#pragma unroll 4
-    for (int g = 0; g < G; ++g) {
-        const size_t cell = (size_t)s * G + g;
-        seg_begin[cell * per + e] = S;
-        if (g < G - 1) S = fmaf(decay2(a2 * seg_dt[cell * channels + c]), S, seg_local[cell * per + e]);
+    // eight segments' folds and step-size sums are fetched before their chain runs: the
+    // chain then waits for one round of loads in eight steps, not for one a step
+    for (int g0 = 0; g0 < G; g0 += 8) {
+        float local[8], sum_dt[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const size_t cell = (size_t)s * G + g0 + j;
+            const bool on = g0 + j < G - 1;
+            local[j] = on ? seg_local[cell * per + e] : 0.0f;
+            sum_dt[j] = on ? seg_dt[cell * channels + c] : 0.0f;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            if (g0 + j < G) {
+                seg_begin[((size_t)s * G + g0 + j) * per + e] = S;
+                S = fmaf(decay2(a2 * sum_dt[j]), S, local[j]);
+            }
+        }
     }
 }
 
