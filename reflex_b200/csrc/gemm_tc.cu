@@ -123,6 +123,17 @@ __device__ __forceinline__ float gated_act(float g, float u, const Fuse& f) {
 //    cache at the row's position.  One launch instead of product + `qkv_post`,
 //    and the 32-bit q/k/v rows never go to memory.  Formulas as in qkv_post.cu.
 
+// The plain epilogue's last step: EPI 5 squares the rectified result, y = max(x W^T, 0)^2
+// (an ungated feed-forward's activation), a template instance of its own beside EPI 0.
+template <int EPI>
+__device__ __forceinline__ float plain_out(float a) {
+    if constexpr (EPI == 5) {
+        const float m = fmaxf(a, 0.0f);
+        return m * m;
+    }
+    return a;
+}
+
 // EPI 0: y = x W^T.  EPI 1: W's rows alternate gate, up (row 2j gate_j, row 2j+1
 // up_j) and y[r, j] = silu(gate_j) * up_j, so the SwiGLU activation costs no
 // launch and no round trip of the [R, 2I] intermediate
@@ -322,6 +333,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const int nkb = max(0, min(num_kb, kb0 + per) - kb0);
     // rows of the tile that each rank of a K-split cluster finishes
     constexpr bool GATED = EPI == 1 || EPI == 4;  // rows alternate gate, up; the epilogue writes their activation
+    constexpr bool PLAIN = EPI == 0 || EPI == 5;  // y = x W^T, EPI 5: y = max(x W^T, 0)^2
     const int mw = GATED ? ((((bm + ksplit - 1) / ksplit) + 1) & ~1) : (bm + ksplit - 1) / ksplit;
 
     if (threadIdx.x == 0) {
@@ -543,7 +555,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     if (threadIdx.x == 64) trace_mark(trace_id, 5);
                 }
                 // Sum in rank order, then the epilogue.
-                if (quads && EPI == 0) {
+                if (quads && PLAIN) {
                     for (int e = et; e < BN * mq; e += ET) {
                         const int rr = e / mq, ml4 = 4 * (e % mq), mm = z * mw + ml4;
                         const int r = r0 + rr, n = n0 + mm;
@@ -560,6 +572,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                             const float f = rstd_s[rr];
                             acc.x *= f, acc.y *= f, acc.z *= f, acc.w *= f;
                         }
+                        if (EPI == 5) acc = make_float4(plain_out<5>(acc.x), plain_out<5>(acc.y), plain_out<5>(acc.z), plain_out<5>(acc.w));
                         if (!dry) store4(y + (size_t)r * N + n, acc);
                     }
                 } else if (quads && GATED) {
@@ -635,7 +648,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                             fuse.ssq_out[(size_t)(r0 + et) * (gridDim.x * ksplit) + blockIdx.x * ksplit + z] = tot;
                         }
                     }
-                } else if (EPI == 0) {
+                } else if (PLAIN) {
                     for (int e = et; e < BN * mw; e += ET) {
                         const int rr = e / mw, ml1 = e % mw, mm = z * mw + ml1;
                         if (mm >= bm) continue;
@@ -643,7 +656,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         for (int p = 0; p < ksplit; ++p) acc += recv[((size_t)p * BN + rr) * mw + ml1];
                         if (PRO) acc *= rstd_s[rr];
                         const int r = r0 + rr;
-                        if (r < R && n0 + mm < N && !dry) rfx::st<TO>(y, (size_t)r * N + n0 + mm, acc);
+                        if (r < R && n0 + mm < N && !dry) rfx::st<TO>(y, (size_t)r * N + n0 + mm, plain_out<EPI>(acc));
                     }
                 } else if (GATED) {
                     const int pw = mw / 2;
@@ -732,8 +745,8 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                             const int rr = c * 16 + j, r = r0 + rr, n = n0 + m;
                             float a = v[j];
                             if (PRO) a *= rstd_s[rr];
-                            if (EPI == 0) {
-                                if (r < R && m < bm && n < N && !dry) rfx::st<TO>(y, (size_t)r * N + n, a);
+                            if (PLAIN) {
+                                if (r < R && m < bm && n < N && !dry) rfx::st<TO>(y, (size_t)r * N + n, plain_out<EPI>(a));
                             } else {
                                 float hv1 = 0.0f;
                                 if (r < R && m < bm && n < N && !dry) {
@@ -1005,6 +1018,18 @@ extern "C" int rfx_gemm_bf16_tc_glu_clamped(const void* x, const void* W, void* 
     f.act_alpha = alpha;
     f.act_limit = limit;
     if (y_dt == RFX_DT_BF16) return dispatch<__nv_bfloat16, 4, false>(x, W, y, R, N, K, ksplit, f, nullptr, err, s);
+    return RFX_ERR_UNSUPPORTED;
+}
+
+// y [R, N] = max(x W^T, 0)^2 as the product's epilogue, for a decode-sized batch (R <= 64).
+extern "C" int rfx_gemm_bf16_tc_relu2(const void* x, const void* W, void* y, int y_dt, int R, int N, int K,
+                                      int ksplit, int* err, void* stream) {
+    if (R <= 0 || N <= 0) return 0;
+    if (int c = check_common(x, W, R, N, K)) return c;
+    if (R > 64) return RFX_ERR_UNSUPPORTED;
+    Fuse f{};
+    if (y_dt == RFX_DT_BF16)
+        return dispatch<__nv_bfloat16, 5, false>(x, W, y, R, N, K, ksplit, f, nullptr, err, (cudaStream_t)stream);
     return RFX_ERR_UNSUPPORTED;
 }
 

@@ -188,14 +188,14 @@ template <typename TY>
 __global__ void __launch_bounds__(256)
 hyper_collapse_kernel(const float* __restrict__ streams, const TY* __restrict__ y, const float* __restrict__ ls,
                       const float* __restrict__ mix, const float* __restrict__ outw, float* __restrict__ out,
-                      int S, int W) {
+                      const int* __restrict__ rows, int S, int W) {
     __shared__ Coef cf;
     pdl_launch_dependents();
     if (y && threadIdx.x < S) cf.out[threadIdx.x] = outw[threadIdx.x];
     if (y && threadIdx.x < S * S) cf.mix[threadIdx.x] = mix[threadIdx.x];
     __syncthreads();
     pdl_wait();
-    const size_t r = blockIdx.x;
+    const size_t r = rows ? (size_t)rows[blockIdx.x] : blockIdx.x;  // out row blockIdx.x is row r of the streams
     const float* xrow = streams + r * S * W;
     const TY* yrow = y ? y + r * W : nullptr;
     for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < W; c += gridDim.y * blockDim.x) {
@@ -205,7 +205,7 @@ hyper_collapse_kernel(const float* __restrict__ streams, const TY* __restrict__ 
 #pragma unroll
         for (int s = 0; s < MAX_S; ++s)
             if (s < S) sum += x[s];
-        out[r * W + c] = sum;
+        out[(size_t)blockIdx.x * W + c] = sum;
     }
 }
 
@@ -280,8 +280,11 @@ extern "C" int rfx_hyper_step(float* streams, const void* y, int y_dt, const flo
     return 0;
 }
 
+// `rows` (may be null): R row indices on the device; out row i is then the sum for row rows[i]
+// of the streams (and of `y`), so that only the rows somebody wants are made.
 extern "C" int rfx_hyper_collapse(const float* streams, const void* y, int y_dt, const float* ls, const float* mix,
-                                  const float* outw, float* out, int R, int S, int W, void* stream) {
+                                  const float* outw, float* out, const int* rows, int R, int S, int W,
+                                  void* stream) {
     if (R <= 0) return 0;
     if (S < 1 || S > MAX_S || W <= 0) return RFX_ERR_UNSUPPORTED;
     if (y && (!mix || !outw)) return RFX_ERR_BAD_ARG;
@@ -291,9 +294,9 @@ extern "C" int rfx_hyper_collapse(const float* streams, const void* y, int y_dt,
     cudaStream_t s = (cudaStream_t)stream;
     if (y && y_dt == RFX_DT_BF16)
         RFX_LAUNCH(hyper_collapse_kernel<__nv_bfloat16>, dim3(R, gy), 256, 0, s, streams, (const __nv_bfloat16*)y, ls,
-                   mix, outw, out, S, W);
+                   mix, outw, out, rows, S, W);
     else
         RFX_LAUNCH(hyper_collapse_kernel<float>, dim3(R, gy), 256, 0, s, streams, (const float*)y, ls, mix, outw,
-                   out, S, W);
+                   out, rows, S, W);
     return 0;
 }

@@ -96,12 +96,17 @@ __device__ __forceinline__ float silu_of(float y) { return y / (1.0f + expf(-y))
 __global__ void __launch_bounds__(256)
 short_conv_kernel(const float* __restrict__ proj, int ld, int col0, const float* __restrict__ bias,
                   const float* __restrict__ w, const float* __restrict__ cbias, int taps,
-                  const float* __restrict__ state, size_t slot_stride, const int* __restrict__ row_slot,
-                  float* __restrict__ out, __nv_bfloat16* __restrict__ out_lo, int C, int by4, int act) {
+                  float* state, size_t slot_stride, const int* __restrict__ row_slot,
+                  float* __restrict__ out, __nv_bfloat16* __restrict__ out_lo, int C, int by4, int act,
+                  int update) {
     pdl_prologue();
     const int r = blockIdx.x;
     const int before = rows_before(row_slot, r, taps - 1);
     const float* tail = state ? state + (size_t)row_slot[r] * slot_stride : nullptr;
+    // `update`: every sequence has one row in this step, so the thread that read a channel's
+    // last inputs is their only reader and moves them on by one (no second launch)
+    float* tail_w = (update && taps > 1 && state) ? state + (size_t)row_slot[r] * slot_stride : nullptr;
+    const int T = taps - 1;
     if (by4) {
         for (int c = 4 * (blockIdx.y * blockDim.x + threadIdx.x); c < C; c += 4 * gridDim.y * blockDim.x) {
             float4 y = conv4_at(proj, ld, col0, c, bias, w, taps, tail, C, r, before);
@@ -112,6 +117,16 @@ short_conv_kernel(const float* __restrict__ proj, int ld, int col0, const float*
             if (act == 1) { y.x = silu_of(y.x); y.y = silu_of(y.y); y.z = silu_of(y.z); y.w = silu_of(y.w); }
             store4(out + (size_t)r * C + c, y);
             if (out_lo) store4(out_lo + (size_t)r * C + c, y);
+            if (tail_w) {
+                for (int i = 0; i + 1 < T; ++i)
+                    store4(tail_w + (size_t)i * C + c, *reinterpret_cast<const float4*>(tail_w + (size_t)(i + 1) * C + c));
+                float4 u = *reinterpret_cast<const float4*>(proj + (size_t)r * ld + col0 + c);
+                if (bias) {
+                    const float4 b = *reinterpret_cast<const float4*>(bias + c);
+                    u.x += b.x; u.y += b.y; u.z += b.z; u.w += b.w;
+                }
+                store4(tail_w + (size_t)(T - 1) * C + c, u);
+            }
         }
         return;
     }
@@ -120,6 +135,10 @@ short_conv_kernel(const float* __restrict__ proj, int ld, int col0, const float*
         if (act == 1) y = silu_of(y);
         out[(size_t)r * C + c] = y;
         if (out_lo) out_lo[(size_t)r * C + c] = __float2bfloat16_rn(y);
+        if (tail_w) {
+            for (int i = 0; i + 1 < T; ++i) tail_w[(size_t)i * C + c] = tail_w[(size_t)(i + 1) * C + c];
+            tail_w[(size_t)(T - 1) * C + c] = proj[(size_t)r * ld + col0 + c] + (bias ? bias[c] : 0.0f);
+        }
     }
 }
 
@@ -221,11 +240,13 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 
 
 // `w`: the filters transposed, [taps][C].  `out_lo` (may be null): the result once
 // more, rounded to bfloat16 (the input of a tensor-core product).
-// `act`: 0 the convolution as it is, 1 silu of it (after `cbias`).
+// `act`: 0 the convolution as it is, 1 silu of it (after `cbias`).  `update` 1: every
+// sequence has exactly one of the R rows, and its last taps - 1 inputs in `state` move on
+// by that row in the same launch (what rfx_conv_state_update does for longer steps).
 extern "C" int rfx_short_conv_act(const float* proj, int ld, int col0, const float* bias, const float* w,
                                   const float* cbias, int taps, const float* state, long long slot_stride,
                                   const int* row_slot, float* out, void* out_lo, int R, int C, int act,
-                                  void* stream) {
+                                  int update, void* stream) {
     if (R <= 0 || C <= 0) return 0;
     if (act != 0 && act != 1) return RFX_ERR_BAD_ARG;
     if (taps < 1 || taps > MAX_TAPS || (taps > 1 && !state)) return RFX_ERR_BAD_ARG;
@@ -236,7 +257,8 @@ extern "C" int rfx_short_conv_act(const float* proj, int ld, int col0, const flo
     // so that a decode step's loads are all in flight at once
     dim3 grid(R, chunks(by4 ? C / (R >= 256 ? 8 : 4) : C, 256));
     RFX_LAUNCH(short_conv_kernel, grid, 256, 0, (cudaStream_t)stream, proj, ld, col0, bias, w, cbias, taps,
-               state, (size_t)slot_stride, row_slot, out, (__nv_bfloat16*)out_lo, C, by4, act);
+               const_cast<float*>(state), (size_t)slot_stride, row_slot, out, (__nv_bfloat16*)out_lo, C, by4, act,
+               update);
     return 0;
 }
 
@@ -244,7 +266,7 @@ extern "C" int rfx_short_conv(const float* proj, int ld, int col0, const float* 
                               const float* cbias, int taps, const float* state, long long slot_stride,
                               const int* row_slot, float* out, void* out_lo, int R, int C, void* stream) {
     return rfx_short_conv_act(proj, ld, col0, bias, w, cbias, taps, state, slot_stride, row_slot, out, out_lo, R,
-                              C, 0, stream);
+                              C, 0, 0, stream);
 }
 
 extern "C" int rfx_conv_qkv_post(const float* proj, int ld, const float* bias, const float* w, int taps,

@@ -132,7 +132,12 @@ class CausalLM:
         return -1 - index
 
     # --- forward ----------------------------------------------------------
-    def hidden_states(self, batch, cache) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+    def hidden_states(self, batch, cache, rows=None) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+        """The residual after the last layer, [rows, hidden] 32-bit, and what is still
+        to be added to it.  `rows` (int32 on the device) asks for those rows only;
+        whether they were cut out says `self.cuts_rows` (a block arrangement that
+        keeps the residual in a form of its own makes the ordinary one at the end,
+        and then only for the rows that are wanted)."""
         ops.prof_mark("start")
         # a token id outside the vocabulary (possible only for ids fed from the device)
         # gives a zero row and sets the device's error word, which `check_errors` reads
@@ -188,8 +193,13 @@ class CausalLM:
         # streams) hands back the ordinary one: [rows, hidden] and a delta or None
         last = self.layers[order[-1].layer] if order else None
         if last is not None and hasattr(last, "finish"):
-            h, pending = last.finish(h, pending)
+            h, pending = last.finish(h, pending, rows=rows)
         return h, pending
+
+    @property
+    def cuts_rows(self) -> bool:
+        order = self.spec.run_order
+        return bool(order) and hasattr(self.layers[order[-1].layer], "finish")
 
     def logits(self, hidden: torch.Tensor, pending, rows: torch.Tensor, rows_host=None) -> torch.Tensor:
         """Final norm and head on the wanted rows only; float32 [len(rows), V]."""
@@ -224,11 +234,14 @@ class CausalLM:
         """For each wanted row the head's logit of one given token id
         (`ids`, int32 on the device, one per wanted row), float32 [wanted]: only
         those rows of the head are read (src/model/dense.rs:2073-2133)."""
-        h, pending = self.hidden_states(batch, cache)
-        out = self.finish_logits(ops.gather_dot(self.normed_rows(h, pending, batch.want_rows), self.head, ids))
+        h, pending = self.hidden_states(batch, cache, rows=batch.want_rows)
+        rows = None if self.cuts_rows else batch.want_rows
+        out = self.finish_logits(ops.gather_dot(self.normed_rows(h, pending, rows), self.head, ids))
         ops.prof_mark("head")
         return out
 
     def forward(self, batch, cache) -> torch.Tensor:
-        h, pending = self.hidden_states(batch, cache)
+        h, pending = self.hidden_states(batch, cache, rows=batch.want_rows)
+        if self.cuts_rows:  # h holds the wanted rows, in order
+            return self.logits(h, pending, None)
         return self.logits(h, pending, batch.want_rows, batch.want_rows_host)

@@ -137,7 +137,7 @@ class Engine:
                     elif n_want:
                         logits = self.model.forward(batch, cache)
                     else:
-                        self.model.hidden_states(batch, cache)
+                        self.model.hidden_states(batch, cache, rows=batch.want_rows)  # nothing wanted: no rows
                         logits = torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
             if self.workspace is not None:
                 self.workspace.settle()

@@ -1090,7 +1090,7 @@ def branch_norm_mean(a: torch.Tensor, a_bias: Optional[torch.Tensor], wa: torch.
 # ------------------------------------------- short convolutions, gated recurrence
 def short_conv(proj: torch.Tensor, col0: int, channels: int, bias: Optional[torch.Tensor], filters_t: torch.Tensor,
                conv_bias: Optional[torch.Tensor], state: Optional[torch.Tensor], batch, also_bf16: bool = False,
-               activation: Optional[str] = None):
+               activation: Optional[str] = None, update_state: bool = False):
     """A causal convolution over time of columns [col0, col0 + channels) of
     `proj` (float32 [R, ld]) plus `bias`, one filter a channel (`filters_t`
     float32 [taps, channels], transposed; the last tap on the current token)
@@ -1098,7 +1098,11 @@ def short_conv(proj: torch.Tensor, col0: int, channels: int, bias: Optional[torc
     n] float32, whose first (taps - 1) * channels floats are the sequence's last
     inputs, oldest first).  float32 [R, channels]; with `also_bf16` a pair, the
     second the same values rounded to bfloat16.  `activation` "silu": y / (1 +
-    e^-y) of the result (after `conv_bias`)."""
+    e^-y) of the result (after `conv_bias`).  `update_state`: the step has one
+    row a sequence, and the launch also moves each sequence's last inputs on by
+    its row (no `conv_state_update` is then needed)."""
+    if update_state and proj.shape[0] != batch.seq_slot.numel():
+        raise InvalidInput("short_conv: update_state is for steps of one row a sequence")
     if activation not in (None, "silu"):
         raise InvalidInput(f"short_conv: activation must be None or 'silu', got {activation!r}")
     R = proj.shape[0]
@@ -1112,7 +1116,7 @@ def short_conv(proj: torch.Tensor, col0: int, channels: int, bias: Optional[torc
         _chk(filters_t, "filters_t", torch.float32), _chk(conv_bias, "conv_bias", torch.float32), taps,
         _chk(state, "state", torch.float32), state.stride(0) if state is not None else 0,
         _chk(batch.row_slot, "row_slot", torch.int32), out.data_ptr(), lo.data_ptr() if lo is not None else 0,
-        R, channels, 1 if activation == "silu" else 0, _stream())
+        R, channels, 1 if activation == "silu" else 0, 1 if update_state else 0, _stream())
     native.check(st, f"short_conv (taps={taps})")
     return (out, lo) if also_bf16 else out
 
@@ -1235,10 +1239,12 @@ def hyper_step(streams: torch.Tensor, write: Optional["StreamWrite"], read: torc
     return out
 
 
-def hyper_collapse(streams: torch.Tensor, write: Optional["StreamWrite"], n_streams: int) -> torch.Tensor:
+def hyper_collapse(streams: torch.Tensor, write: Optional["StreamWrite"], n_streams: int,
+                   rows: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The sum of the residual streams after `write` (if any), float32 [R, W];
-    `streams` itself is left as it is."""
-    R = streams.shape[0]
+    `streams` itself is left as it is.  `rows` (int32 on the device): only those
+    rows, in that order, [len(rows), W]."""
+    R = streams.shape[0] if rows is None else rows.numel()
     S = int(n_streams)
     W = streams.shape[1] // S
     out = _new((R, W), torch.float32, streams.device, keep=True)
@@ -1247,7 +1253,8 @@ def hyper_collapse(streams: torch.Tensor, write: Optional["StreamWrite"], n_stre
         _chk(streams, "streams", torch.float32), _chk(y, "y"), dt_code(y.dtype) if y is not None else 0,
         _chk(write.scale, "scale", torch.float32) if write is not None else 0,
         _chk(write.mix, "mix", torch.float32) if write is not None else 0,
-        _chk(write.out, "out", torch.float32) if write is not None else 0, out.data_ptr(), R, S, W, _stream())
+        _chk(write.out, "out", torch.float32) if write is not None else 0, out.data_ptr(),
+        _chk(rows, "rows", torch.int32), R, S, W, _stream())
     native.check(st, f"hyper_collapse (streams={S}, width={W})")
     return out
 
@@ -1273,7 +1280,20 @@ def relu2_(a: torch.Tensor) -> torch.Tensor:
 
 
 def linear_relu2(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
-    """relu(x @ W.T)^2, [R, I] in x's dtype: product, then the activation in place."""
+    """relu(x @ W.T)^2, [R, I] in x's dtype.  For a few bfloat16 rows the
+    activation is the product kernel's epilogue (on the 32-bit sums, rounded
+    once); otherwise product, then the activation in place."""
+    R, K = x.shape
+    if x.dtype == torch.bfloat16 and R <= GEMV_MAX_ROWS and K % 8 == 0 and FUSE_GLU:
+        N = weight.shape[0]
+        _chk(x, "x", torch.bfloat16)
+        _chk(weight, "weight", torch.bfloat16)
+        y = _new((R, N), torch.bfloat16, x.device)
+        st = native.lib().rfx_gemm_bf16_tc_relu2(
+            x.data_ptr(), weight.data_ptr(), y.data_ptr(), BF16, R, N, K, 0,
+            device_error_word(x.device).data_ptr(), _stream())
+        native.check(st, f"gemm_bf16_tc_relu2 (R={R}, N={N}, K={K})")
+        return y
     return relu2_(linear(x, weight))
 
 

@@ -32,6 +32,7 @@ _SIGNATURES = {
                          c_int, c_int, c_float, c_void_p, c_void_p],
     "rfx_gemm_bf16_tc_glu_clamped": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
                                      c_float, c_void_p, c_void_p],
+    "rfx_gemm_bf16_tc_relu2": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "rfx_gemm_bf16_tc_residual": [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
                                   c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "rfx_gemm_bf16_tc_qkv": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_float, c_void_p, c_void_p,
@@ -57,13 +58,13 @@ _SIGNATURES = {
                         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
                         c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "rfx_short_conv_act": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_longlong,
-                           c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+                           c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "rfx_sigmoid_gate_mul": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "rfx_hyper_expand": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "rfx_hyper_step": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float,
                        c_float, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
-    "rfx_hyper_collapse": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                           c_void_p],
+    "rfx_hyper_collapse": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                           c_int, c_void_p],
     "rfx_mamba_scan": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int,
                        c_void_p, c_void_p, c_void_p, c_longlong, c_longlong, c_void_p, c_void_p, c_int, c_int,
                        c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],

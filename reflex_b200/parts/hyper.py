@@ -142,9 +142,10 @@ class HyperPreNormBlock:
             write = ops.StreamWrite(y, self.scale[q], self.mix[q], self.write[q])
         return hidden, write
 
-    def finish(self, hidden: torch.Tensor, pending):
+    def finish(self, hidden: torch.Tensor, pending, rows=None):
         """After the last layer: the last write, then the sum of the streams, as
-        the ordinary residual [rows, hidden] with nothing left to add."""
-        out = ops.hyper_collapse(hidden, self._pending_write(hidden, pending), self.streams)
+        the ordinary residual [rows, hidden] with nothing left to add.  With
+        `rows` (int32 on the device) only those rows are made, in that order."""
+        out = ops.hyper_collapse(hidden, self._pending_write(hidden, pending), self.streams, rows)
         ops.prof_mark("norm")
         return out, None

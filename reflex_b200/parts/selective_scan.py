@@ -85,11 +85,14 @@ class SelectiveScan:
         lo = self.dtype == torch.bfloat16
         xz = ops.linear(x, self.w_in, out_dtype=torch.float32)  # [rows, x | z]
         ops.prof_mark("qkv_gemm")
+        # a row a sequence (decoding): the convolution's launch also moves the last inputs on
+        single = xz.shape[0] == batch.seq_slot.numel()
         u = ops.short_conv(xz, 0, C, None, self.filters, self.conv_bias, state if self.taps > 1 else None, batch,
-                           also_bf16=lo, activation="silu")
+                           also_bf16=lo, activation="silu", update_state=single and self.taps > 1)
         u, u_in = u if lo else (u, u)
-        # the sequences' new last inputs (the rows that read the old ones are done: the launch above)
-        ops.conv_state_update(xz, 0, C, None, self.taps, state, batch)
+        if not single:
+            # the sequences' new last inputs (the rows that read the old ones are done: the launch above)
+            ops.conv_state_update(xz, 0, C, None, self.taps, state, batch)
         ops.prof_mark("conv_post")
         bc = ops.linear(u_in, self.w_x_bc, out_dtype=torch.float32)  # [rows, B | C]
         dt_low = ops.linear(u_in, self.w_x_dt, out_dtype=self.dtype)  # [rows, R]

@@ -22,7 +22,7 @@ def f32(a):
 
 
 # ------------------------------------------------------------- mechanisms
-@pytest.mark.parametrize("S,W,R", [(1, 64, 3), (2, 100, 5), (3, 320, 70), (4, 4096, 2), (8, 72, 9)])
+@pytest.mark.parametrize("S,W,R", [(1, 64, 3), (2, 100, 5), (3, 328, 70), (4, 4096, 2), (8, 72, 9)])
 @pytest.mark.parametrize("y_dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 def test_streams_write_read_norm_and_sum(S, W, R, y_dtype, out_dtype):
@@ -131,7 +131,7 @@ KEPT_CASES = [  # nq, nkv, d, [(start, n_new)], window, keep_first
     (6, 1, 64, [(0, 400), (328, 4)], 200, 130),            # into a third; position 329 is the first to lose one
     (8, 2, 128, [(0, 150), (200, 40)], 33, 1),
     (3, 3, 40, [(0, 140)], 64, 0),                         # a window of a page, nothing kept
-    (6, 3, 128, [(0, 300)], 136, 4),
+    (12, 3, 128, [(0, 300)], 150, 5),
     (4, 4, 32, [(0, 100), (30, 50)], 5, 64),               # more kept than the window is long
 ]
 
@@ -204,7 +204,7 @@ def test_a_window_that_keeps_the_first_tokens_in_every_attention_kernel(kernel, 
                                              (torch.bfloat16, torch.bfloat16)])
 def test_sigmoid_gate_from_columns_of_a_wider_row_and_squared_relu(a_dtype, z_dtype):
     g = torch.Generator().manual_seed(5)
-    for R, H, col, ld in ((1, 768, 1152, 1920), (70, 52, 9, 70), (9, 4096, 0, 4096)):
+    for R, H, col, ld in ((1, 640, 896, 1600), (70, 52, 9, 70), (9, 4096, 0, 4096)):
         a = torch.randn(R, H, generator=g).to(a_dtype)
         z = (torch.randn(R, ld, generator=g) * 4).to(z_dtype)
         ref = a.double().numpy() * pp.sigmoid(z[:, col:col + H].double().numpy())
@@ -215,9 +215,24 @@ def test_sigmoid_gate_from_columns_of_a_wider_row_and_squared_relu(a_dtype, z_dt
             (1e-6 if a_dtype == torch.float32 else 8e-3)
 
 
+@pytest.mark.parametrize("R,N,K", [(1, 96, 64), (8, 1000, 328), (33, 256, 2048), (64, 136, 72), (65, 64, 64)])
+def test_squared_relu_as_the_products_epilogue(R, N, K):
+    """A few bfloat16 rows: the activation rides in the product kernel; beyond, apart."""
+    g = torch.Generator().manual_seed(R + N)
+    x = torch.randn(R, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    prod = x.double().numpy() @ w.double().numpy().T
+    ref = np.maximum(prod, 0.0) ** 2
+    out = ops().linear_relu2(x.to(DEV), w.to(DEV))
+    assert out.dtype == torch.bfloat16 and tuple(out.shape) == (R, N)
+    assert relerr(out, ref) < 8e-3
+    # the signs: where the product is clearly negative the result is exactly zero
+    assert bool((out.cpu().double().numpy()[prod < -1e-2] == 0.0).all())
+
+
 # rows per sequence and step; the first step is long enough for the scan to cut its sequences
 # into segments (also the one of nine rows), the last but one for one sequence in three
-CUTS = ({0: 197, 1: 9, 2: 81}, {0: 1, 2: 2}, {2: 1}, {0: 2, 2: 14}, {2: 115}, {0: 30})
+CUTS = ({0: 197, 1: 9, 2: 81}, {0: 1, 2: 2}, {2: 1}, {0: 2, 2: 14}, {2: 1, 0: 1}, {2: 115}, {0: 1, 2: 1}, {0: 30})
 
 
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
@@ -233,7 +248,7 @@ def test_filter_silu_and_scan_carried_through_their_state(C, N, taps, out_dtype,
     16 bytes where the sizes allow it; 1: none)."""
     g = torch.Generator().manual_seed(C + N)
     b_off, c_off, ld_bc = gap, N + 2 * gap, 2 * N + 3 * gap
-    lens, slots = {0: 230, 1: 9, 2: 213}, {0: 3, 1: 0, 2: 6}
+    lens, slots = {0: 232, 1: 9, 2: 215}, {0: 3, 1: 0, 2: 6}
     ld_z, z_off = 2 * C + 4, C + 4
     xz = {s: torch.randn(n, ld_z, generator=g) for s, n in lens.items()}
     dtpre = {s: torch.randn(n, C, generator=g) * 3 for s, n in lens.items()}
@@ -251,9 +266,11 @@ def test_filter_silu_and_scan_carried_through_their_state(C, N, taps, out_dtype,
         b = FakeBatch([[0] * cuts[s] for s in ids], [slots[s] for s in ids], [fed[s] for s in ids])
         cat = lambda d: torch.cat([d[s][fed[s]:fed[s] + cuts[s]] for s in ids]).to(DEV).contiguous()  # noqa: E731
         rows = cat(xz)
+        single = all(n == 1 for n in cuts.values())  # a row a sequence: the filter's launch moves its state on
         u = ops().short_conv(rows, 0, C, None, w.t().contiguous().to(DEV), cb.to(DEV), state if taps > 1 else None, b,
-                             activation="silu")
-        ops().conv_state_update(rows, 0, C, None, taps, state, b)
+                             activation="silu", update_state=single and taps > 1)
+        if not single:
+            ops().conv_state_update(rows, 0, C, None, taps, state, b)
         y = ops().mamba_scan(u, cat(dtpre), dtb.to(DEV), cat(bc), b_off, c_off, rows, z_off, A.to(DEV).contiguous(),
                              D.to(DEV), state, (taps - 1) * C, b, out_dtype)
         for j, s in enumerate(ids):
