@@ -52,6 +52,11 @@ def test_streams_write_read_norm_and_sum(S, W, R, y_dtype, out_dtype):
     assert relerr(out, pp.norm_one_plus(pp.hyper_read(new, win.double().numpy()), nw.double().numpy(), 1e-5)) < tol
     assert relerr(total, new.sum(axis=0)) < 3e-6
     assert relerr(ops().hyper_collapse(xs, None, S), new.sum(axis=0)) < 3e-6
+    # only some rows, in an order of their own, with the write still to come
+    pick = [R - 1, 0, R // 2]
+    xs3 = torch.tensor(ref.transpose(1, 0, 2).reshape(R, S * W), dtype=torch.float32, device=DEV)
+    some = ops().hyper_collapse(xs3, write, S, rows=i32(pick))
+    assert tuple(some.shape) == (3, W) and relerr(some, new.sum(axis=0)[pick]) < 3e-6
     # no scale: y as it is
     xs2 = torch.tensor(ref.transpose(1, 0, 2).reshape(R, S * W), dtype=torch.float32, device=DEV)
     write = ops().StreamWrite(y.to(DEV), None, mix.to(DEV).contiguous(), wout.to(DEV))
