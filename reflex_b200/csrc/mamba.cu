@@ -55,6 +55,34 @@ __device__ __forceinline__ float decay2(float v) {
     return r;
 }
 
+// The step size's last product inside the row-by-row form: channel c's row of W_dt
+// ([channels][rank], bfloat16 or 32-bit) times the row's low-rank vector, shared by the
+// channel's lanes and met by shuffles.  With bfloat16 weights the vector is rounded to
+// bfloat16 first, as the product kernel's input would be.
+struct StepRank {
+    const void* w;     // null: the step sizes come ready in `dtpre`
+    int bf16;          // the weights' type
+    int rank;
+    int off;           // the vector's first column in the B | C rows
+};
+
+__device__ __forceinline__ float step_from_rank(const StepRank& sr, int c, const float* __restrict__ low, int sub,
+                                                int lpc) {
+    float acc = 0.0f;
+    if (sr.bf16) {
+        const __nv_bfloat16* wr = reinterpret_cast<const __nv_bfloat16*>(sr.w) + (size_t)c * sr.rank;
+#pragma unroll 4
+        for (int j = sub; j < sr.rank; j += lpc)
+            acc = fmaf(__bfloat162float(wr[j]), __bfloat162float(__float2bfloat16_rn(low[j])), acc);
+    } else {
+        const float* wr = reinterpret_cast<const float*>(sr.w) + (size_t)c * sr.rank;
+#pragma unroll 4
+        for (int j = sub; j < sr.rank; j += lpc) acc = fmaf(wr[j], low[j], acc);
+    }
+    for (int o = lpc >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    return acc;
+}
+
 template <typename TO, int NPL>
 __global__ void __launch_bounds__(THREADS)
 mamba_scan_kernel(const float* __restrict__ x, const float* __restrict__ dtpre, const float* __restrict__ dt_bias,
@@ -62,7 +90,7 @@ mamba_scan_kernel(const float* __restrict__ x, const float* __restrict__ dtpre, 
                   const float* __restrict__ zsrc, int ld_z, int z_off, const float* __restrict__ A,
                   const float* __restrict__ Dw, float* __restrict__ state, size_t slot_stride, size_t state_off,
                   const int* __restrict__ seq_slot, const int* __restrict__ seq_row0, TO* __restrict__ out,
-                  int channels, int N, int lpc) {
+                  int channels, int N, int lpc, StepRank sr) {
     pdl_launch_dependents();
     const int s = blockIdx.x;
     const int sub = threadIdx.x % lpc;                       // which share of the channel's states
@@ -92,9 +120,9 @@ mamba_scan_kernel(const float* __restrict__ x, const float* __restrict__ dtpre, 
     auto fetch = [&](int t) {
         const size_t r = (size_t)(row0 + t);
         xv = x[r * channels + cc];
-        dv = dtpre[r * channels + cc];
         zv = zsrc[r * ld_z + z_off + cc];
         const float* brow = bc + r * ld_bc;
+        dv = sr.w ? step_from_rank(sr, cc, brow + sr.off, sub, lpc) : dtpre[r * channels + cc];
 #pragma unroll
         for (int i = 0; i < NPL; ++i) {
             const int n = sub + i * lpc;
@@ -413,16 +441,33 @@ extern "C" long long rfx_mamba_scan_scratch(int S, int R, int channels, int N) {
 // [slots][slot_stride] floats, this mixer's S at `state_off`.  R rows in all, of S
 // sequences: steps of four rows a sequence and more take the tiled form, which
 // wants `scratch` (rfx_mamba_scan_scratch floats) when it cuts sequences into segments.
+// `w_dt` (may be null; then `dtpre` holds the step sizes before their bias): W_dt
+// [channels][rank] of type `w_dt_type`; the rows of `bc` hold the low-rank vector at
+// column `low_off`, and dtpre = W_dt . vector is made here (row-by-row form only).
 extern "C" int rfx_mamba_scan(const float* x, const float* dtpre, const float* dt_bias, const float* bc,
                               int ld_bc, int b_off, int c_off, const float* zsrc, int ld_z, int z_off,
                               const float* A, const float* Dw, float* state, long long slot_stride,
                               long long state_off, const int* seq_slot, const int* seq_row0, int S, int R,
-                              void* out, int out_dt, int channels, int N, float* scratch, void* stream) {
+                              void* out, int out_dt, int channels, int N, float* scratch, const void* w_dt,
+                              int w_dt_type, int rank, int low_off, void* stream) {
     if (S <= 0 || channels <= 0) return 0;
     if (N < 1 || N > 512) return RFX_ERR_UNSUPPORTED;
     if (out_dt != RFX_DT_F32 && out_dt != RFX_DT_BF16) return RFX_ERR_BAD_ARG;
     cudaStream_t st = (cudaStream_t)stream;
     const ScanPlan plan = scan_plan(S, R, channels, N);
+    StepRank sr{};
+    if (w_dt) {
+        // the step sizes' last product rides in the row-by-row form only
+        if (plan.G >= 1) return RFX_ERR_UNSUPPORTED;
+        if ((w_dt_type != RFX_DT_F32 && w_dt_type != RFX_DT_BF16) || rank < 1 || low_off < 0 || low_off + rank > ld_bc)
+            return RFX_ERR_BAD_ARG;
+        sr.w = w_dt;
+        sr.bf16 = w_dt_type == RFX_DT_BF16;
+        sr.rank = rank;
+        sr.off = low_off;
+    } else if (!dtpre) {
+        return RFX_ERR_BAD_ARG;
+    }
     if (plan.G >= 1) {
         const int lpc = plan.lpc, CH = THREADS / lpc, TT = plan.TT, G = plan.G;
         const int npl = (N + lpc - 1) / lpc;
@@ -484,7 +529,7 @@ extern "C" int rfx_mamba_scan(const float* x, const float* dtpre, const float* d
 #define RFX_SCAN(TO, P)                                                                                       \
     RFX_LAUNCH((mamba_scan_kernel<TO, P>), grid, THREADS, 0, st, x, dtpre, dt_bias, bc, ld_bc, b_off, c_off, \
                zsrc, ld_z, z_off, A, Dw, state, (size_t)slot_stride, (size_t)state_off, seq_slot, seq_row0,  \
-               (TO*)out, channels, N, lpc)
+               (TO*)out, channels, N, lpc, sr)
 #define RFX_SCAN_N(TO)                       \
     do {                                     \
         if (npl <= 1) RFX_SCAN(TO, 1);       \

@@ -181,6 +181,37 @@ sigmoid_gate_mul_kernel(TA* __restrict__ a, const TZ* __restrict__ z, int ldz, i
     }
 }
 
+// the same for bfloat16 `a`, four neighbouring elements a thread (8-byte accesses of `a`, 8 or
+// 16 of `z`); H, ldz and col multiples of four
+template <typename TZ>
+__global__ void __launch_bounds__(256)
+sigmoid_gate_mul4_kernel(__nv_bfloat16* __restrict__ a, const TZ* __restrict__ z, int ldz, int col, int H) {
+    pdl_prologue();
+    const size_t r = blockIdx.x;
+    for (int c = 4 * (blockIdx.y * blockDim.x + threadIdx.x); c < H; c += 4 * gridDim.y * blockDim.x) {
+        float g[4];
+        if constexpr (sizeof(TZ) == 4) {
+            const float4 v = *reinterpret_cast<const float4*>(z + r * ldz + col + c);
+            g[0] = v.x, g[1] = v.y, g[2] = v.z, g[3] = v.w;
+        } else {
+            const uint2 v = *reinterpret_cast<const uint2*>(z + r * ldz + col + c);
+            const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+            const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+            g[0] = lo.x, g[1] = lo.y, g[2] = hi.x, g[3] = hi.y;
+        }
+        uint2 av = *reinterpret_cast<const uint2*>(a + r * H + c);
+        float2 a0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&av.x));
+        float2 a1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&av.y));
+        a0.x = a0.x / (1.0f + expf(-g[0]));
+        a0.y = a0.y / (1.0f + expf(-g[1]));
+        a1.x = a1.x / (1.0f + expf(-g[2]));
+        a1.y = a1.y / (1.0f + expf(-g[3]));
+        *reinterpret_cast<__nv_bfloat162*>(&av.x) = __floats2bfloat162_rn(a0.x, a0.y);
+        *reinterpret_cast<__nv_bfloat162*>(&av.y) = __floats2bfloat162_rn(a1.x, a1.y);
+        *reinterpret_cast<uint2*>(a + r * H + c) = av;
+    }
+}
+
 // blocks along a row for kernels that take a row's elements independently: few rows get a
 // thread an element (every load in flight at once), many rows walk their row
 int row_chunks(int R, int H) {
@@ -278,6 +309,17 @@ extern "C" int rfx_sigmoid_gate_mul(void* a, int a_dt, const void* z, int z_dt, 
     if (R <= 0 || H <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     const dim3 grid(R, row_chunks(R, H));
+    const bool by4 = a_dt == RFX_DT_BF16 && H % 4 == 0 && ldz % 4 == 0 && col % 4 == 0 &&
+                     (reinterpret_cast<uintptr_t>(a) & 7) == 0 && (reinterpret_cast<uintptr_t>(z) & 15) == 0;
+    if (by4 && (z_dt == RFX_DT_F32 || z_dt == RFX_DT_BF16)) {
+        const dim3 grid4(R, row_chunks(R, H / 4));
+        if (z_dt == RFX_DT_F32)
+            RFX_LAUNCH(sigmoid_gate_mul4_kernel<float>, grid4, 256, 0, s, (__nv_bfloat16*)a, (const float*)z, ldz, col, H);
+        else
+            RFX_LAUNCH(sigmoid_gate_mul4_kernel<__nv_bfloat16>, grid4, 256, 0, s, (__nv_bfloat16*)a,
+                       (const __nv_bfloat16*)z, ldz, col, H);
+        return 0;
+    }
     if (a_dt == RFX_DT_F32 && z_dt == RFX_DT_F32)
         RFX_LAUNCH((sigmoid_gate_mul_kernel<float, float>), grid, 256, 0, s, (float*)a, (const float*)z, ldz, col, H);
     else if (a_dt == RFX_DT_BF16 && z_dt == RFX_DT_F32)

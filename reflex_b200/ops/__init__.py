@@ -1300,17 +1300,28 @@ def linear_relu2(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
 # ------------------------------------------------------------- selective scan
 def mamba_scan(x: torch.Tensor, dtpre: torch.Tensor, dt_bias: Optional[torch.Tensor], bc: torch.Tensor, b_off: int,
                c_off: int, z: torch.Tensor, z_off: int, A: torch.Tensor, D: Optional[torch.Tensor],
-               state: torch.Tensor, state_off: int, batch, out_dtype: torch.dtype) -> torch.Tensor:
+               state: torch.Tensor, state_off: int, batch, out_dtype: torch.dtype,
+               dt_weight: Optional[torch.Tensor] = None, dt_low_off: int = 0) -> torch.Tensor:
     """The selective scan over the step's rows, sequence by sequence
     (csrc/mamba.cu): `x`, `dtpre` float32 [R, channels]; `bc` float32 rows with B
     at column `b_off` and C at `c_off` (N each); `z` float32 rows with the gate's
     pre-activation at `z_off`; `A` float32 [channels, N]; the running state is
     `state[slot, state_off : state_off + channels * N]`.  Returns (S . C + D x) *
-    silu(z), [R, channels] in `out_dtype`."""
+    silu(z), [R, channels] in `out_dtype`.  With `dt_weight` ([channels, rank],
+    float32 or bfloat16; steps of a row or two a sequence only) `dtpre` is None:
+    the rows of `bc` hold the step sizes' low-rank vector at column `dt_low_off`
+    and the kernel makes dtpre = dt_weight . vector itself (the vector rounded to
+    bfloat16 first where the weights are bfloat16)."""
     R, C = x.shape
     N = A.shape[1]
-    if tuple(dtpre.shape) != (R, C) or A.shape[0] != C:
-        raise InvalidInput("mamba_scan: x and dtpre must be [rows, channels] and A [channels, states]")
+    if dt_weight is None:
+        if dtpre is None or tuple(dtpre.shape) != (R, C):
+            raise InvalidInput("mamba_scan: dtpre must be [rows, channels]")
+    elif dt_weight.shape[0] != C or dt_low_off + dt_weight.shape[1] > bc.shape[1] or \
+            dt_weight.dtype not in (torch.float32, torch.bfloat16):
+        raise InvalidInput("mamba_scan: dt_weight must be [channels, rank] and its vector fit into the rows of bc")
+    if A.shape[0] != C or x.dtype != torch.float32:
+        raise InvalidInput("mamba_scan: x must be float32 [rows, channels] and A [channels, states]")
     if max(b_off, c_off) + N > bc.shape[1] or z_off + C > z.shape[1]:
         raise InvalidInput("mamba_scan: B, C or z do not fit into their rows")
     out = _new((R, C), out_dtype, x.device)
@@ -1325,7 +1336,8 @@ def mamba_scan(x: torch.Tensor, dtpre: torch.Tensor, dt_bias: Optional[torch.Ten
         _chk(state, "state", torch.float32), state.stride(0), int(state_off),
         _chk(batch.seq_slot, "seq_slot", torch.int32), _chk(batch.seq_row0, "seq_row0", torch.int32),
         n_seq, R, out.data_ptr(), dt_code(out_dtype), C, N, scratch.data_ptr() if scratch is not None else None,
-        _stream())
+        _chk(dt_weight, "dt_weight"), dt_code(dt_weight.dtype) if dt_weight is not None else 0,
+        dt_weight.shape[1] if dt_weight is not None else 0, int(dt_low_off), _stream())
     native.check(st, f"mamba_scan (channels={C}, states={N})")
     return out
 

@@ -67,7 +67,7 @@ _SIGNATURES = {
                            c_int, c_void_p],
     "rfx_mamba_scan": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int,
                        c_void_p, c_void_p, c_void_p, c_longlong, c_longlong, c_void_p, c_void_p, c_int, c_int,
-                       c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
+                       c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "rfx_attention_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
                              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
                              c_void_p, c_longlong, c_void_p, c_void_p],

@@ -41,7 +41,7 @@ class SelectiveScan:
         self.states = int(spec.param("state"))
         self.rank = int(spec.param("dt_rank"))
         self.taps = int(spec.param("taps", 1))
-        self.w_in = self.filters = self.conv_bias = self.w_x_dt = self.w_x_bc = self.w_dt = self.dt_bias = None
+        self.w_in = self.filters = self.conv_bias = self.w_x = self.w_x_dt = self.w_x_bc = self.w_dt = self.dt_bias = None
         self.A = self.D = self.o = None
 
     @classmethod
@@ -74,6 +74,9 @@ class SelectiveScan:
         # result is the next product's input (compute type), the second's enters the scan (32-bit)
         w_x = dev(tensors["x_proj"])
         self.w_x_dt, self.w_x_bc = w_x[: self.rank].contiguous(), w_x[self.rank:].contiguous()
+        # and whole, [dt | B | C]: a row a sequence takes one product, its step sizes' last
+        # product rides in the scan
+        self.w_x = w_x.contiguous()
         self.w_dt = dev(tensors["dt_proj"])
         self.dt_bias = f32(tensors["dt_bias"])
         self.A = (-torch.exp(f32(tensors["A_log"]))).contiguous()  # made once: the weights do not change
@@ -94,12 +97,19 @@ class SelectiveScan:
             # the sequences' new last inputs (the rows that read the old ones are done: the launch above)
             ops.conv_state_update(xz, 0, C, None, self.taps, state, batch)
         ops.prof_mark("conv_post")
-        bc = ops.linear(u_in, self.w_x_bc, out_dtype=torch.float32)  # [rows, B | C]
-        dt_low = ops.linear(u_in, self.w_x_dt, out_dtype=self.dtype)  # [rows, R]
-        dtpre = ops.linear(dt_low, self.w_dt, out_dtype=torch.float32)  # [rows, inner], before the bias
-        ops.prof_mark("scan_proj")
-        y = ops.mamba_scan(u, dtpre, self.dt_bias, bc, 0, N, xz, C, self.A, self.D, state,
-                           (self.taps - 1) * C, batch, self.dtype)
+        if single:
+            # decoding: one product [rows, dt | B | C] in 32-bit; W_dt meets its vector in the scan
+            proj = ops.linear(u_in, self.w_x, out_dtype=torch.float32)
+            ops.prof_mark("scan_proj")
+            y = ops.mamba_scan(u, None, self.dt_bias, proj, self.rank, self.rank + N, xz, C, self.A, self.D, state,
+                               (self.taps - 1) * C, batch, self.dtype, dt_weight=self.w_dt, dt_low_off=0)
+        else:
+            bc = ops.linear(u_in, self.w_x_bc, out_dtype=torch.float32)  # [rows, B | C]
+            dt_low = ops.linear(u_in, self.w_x_dt, out_dtype=self.dtype)  # [rows, R]
+            dtpre = ops.linear(dt_low, self.w_dt, out_dtype=torch.float32)  # [rows, inner], before the bias
+            ops.prof_mark("scan_proj")
+            y = ops.mamba_scan(u, dtpre, self.dt_bias, bc, 0, N, xz, C, self.A, self.D, state,
+                               (self.taps - 1) * C, batch, self.dtype)
         ops.prof_mark("scan")
         out = ops.linear(y, self.o, out_dtype=torch.float32)
         ops.prof_mark("o_proj")

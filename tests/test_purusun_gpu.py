@@ -305,6 +305,44 @@ def test_filter_silu_and_scan_carried_through_their_state(C, N, taps, out_dtype,
     assert relerr(y, ref(1)) < tol
 
 
+@pytest.mark.parametrize("w_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("C,N,rank,rows", [(48, 8, 4, 1), (24, 1, 1, 1), (50, 5, 3, 1), (256, 64, 8, 1), (16, 130, 2, 1),
+                                           (40, 16, 128, 2)])
+def test_step_sizes_from_their_low_rank_vector_inside_the_scan(C, N, rank, rows, w_dtype):
+    """A row or two a sequence: the rows hold [vector | B | C]; the kernel makes
+    W_dt . vector itself (the vector rounded to bfloat16 where the weights are)."""
+    g = torch.Generator().manual_seed(C * 7 + N)
+    n_seq, ld = 3, rank + 2 * N
+    R = n_seq * rows
+    u, xz = torch.randn(R, C, generator=g), torch.randn(R, 2 * C, generator=g)
+    proj = torch.randn(R, ld, generator=g)
+    w_dt = (torch.randn(C, rank, generator=g) * 2 / math.sqrt(rank)).to(w_dtype)
+    dtb, A = torch.randn(C, generator=g), -torch.exp(torch.randn(C, N, generator=g) * 0.7)
+    D = torch.randn(C, generator=g)
+    state0 = torch.randn(4, C * N + 3, generator=g)
+    b = FakeBatch([[0] * rows] * n_seq, [2, 0, 3], [5, 6, 7])
+    low = proj[:, :rank].to(w_dtype).double().numpy()
+    dtpre = low @ w_dt.double().numpy().T
+    st1, st2 = state0.clone().to(DEV), state0.clone().to(DEV)
+    got = ops().mamba_scan(u.to(DEV), None, dtb.to(DEV), proj.to(DEV), rank, rank + N, xz.to(DEV), C,
+                           A.to(DEV).contiguous(), D.to(DEV), st1, 0, b, torch.float32, dt_weight=w_dt.to(DEV),
+                           dt_low_off=0)
+    want = ops().mamba_scan(u.to(DEV), torch.tensor(dtpre, dtype=torch.float32, device=DEV), dtb.to(DEV), proj.to(DEV),
+                            rank, rank + N, xz.to(DEV), C, A.to(DEV).contiguous(), D.to(DEV), st2, 0, b, torch.float32)
+    assert relerr(got, want.double().cpu().numpy()) < 2e-5
+    assert relerr(st1, st2.double().cpu().numpy()) < 2e-5
+    # and against the recurrence written out, from the states the slots held
+    for j, slot in enumerate([2, 0, 3]):
+        S = state0[slot, :C * N].double().numpy().reshape(C, N).copy()
+        for t in range(rows):
+            r = j * rows + t
+            dt = pp.softplus(dtpre[r] + dtb.double().numpy())
+            S = np.exp(dt[:, None] * A.double().numpy()) * S + (dt * u[r].double().numpy())[:, None] * \
+                proj[r, rank:rank + N].double().numpy()[None, :]
+            y = S @ proj[r, rank + N:].double().numpy() + D.double().numpy() * u[r].double().numpy()
+            assert relerr(got[r], y * pp.silu(xz[r, C:].double().numpy())) < 2e-5, (slot, t)
+
+
 def test_a_slow_decay_keeps_a_far_input_and_a_fast_one_forgets_it():
     """One large input at the first token, 600 tokens of nothing after it: the
     channel whose decay is nearly one still holds it, the fast one has lost it;
