@@ -196,9 +196,23 @@ struct ScanPlan {
     int G;         // segments a sequence
 };
 
+// softplus and silu of a (row, channel), once a tile.  FAST (results that are rounded to
+// bfloat16): the hardware's exponential, logarithm and division, about 1e-6 of the value.
+template <bool FAST> __device__ __forceinline__ float softplus_t(float v) {
+    if constexpr (FAST) {
+        const float e = __expf(-fabsf(v));
+        return fmaxf(v, 0.0f) + (e < 1e-4f ? e : __logf(1.0f + e));
+    }
+    return softplus_f(v);
+}
+template <bool FAST> __device__ __forceinline__ float silu_t(float z) {
+    if constexpr (FAST) return __fdividef(z, 1.0f + __expf(-z));
+    return z / (1.0f + expf(-z));
+}
+
 // V floats a copy: 4 where every address involved is a multiple of 16 bytes, else 1.
-// FOLD: step (1), no output; else step (3).
-template <typename TO, int NPL, int V, bool FOLD>
+// FOLD: step (1), no output; else step (3).  FAST: see above; both steps of a scan take the same.
+template <typename TO, int NPL, int V, bool FOLD, bool FAST>
 __global__ void __launch_bounds__(THREADS)
 mamba_scan_tiled_kernel(const float* __restrict__ x, const float* __restrict__ dtpre,
                         const float* __restrict__ dt_bias, const float* __restrict__ bc, int ld_bc, int b_off,
@@ -298,11 +312,8 @@ mamba_scan_tiled_kernel(const float* __restrict__ x, const float* __restrict__ d
         // (a thread meets the same channel every time: the block's threads are a multiple of CH)
         for (int i = threadIdx.x; i < valid * CH; i += THREADS) {
             if (!mine_live) break;
-            ds[i] = softplus_f(ds[i] + mine_bias);
-            if (!FOLD) {
-                const float zt = zs[i];
-                zs[i] = zt / (1.0f + expf(-zt));
-            }
+            ds[i] = softplus_t<FAST>(ds[i] + mine_bias);
+            if (!FOLD) zs[i] = silu_t<FAST>(zs[i]);
         }
         __syncthreads();
         // (B) the recurrence: per row NPL independent multiply-adds on S
@@ -483,38 +494,42 @@ extern "C" int rfx_mamba_scan(const float* x, const float* dtpre, const float* d
         const bool wide = channels % 4 == 0 && N % 4 == 0 && ld_bc % 4 == 0 && b_off % 4 == 0 && c_off % 4 == 0 &&
                           ld_z % 4 == 0 && z_off % 4 == 0 && aligned(x) && aligned(dtpre) && aligned(bc) &&
                           aligned(zsrc);
-#define RFX_TILED(TO, P, V, FOLD)                                                                                 \
+#define RFX_TILED(TO, P, V, FOLD, FAST)                                                                           \
     do {                                                                                                          \
         if (smem > 48 * 1024)                                                                                     \
-            cudaFuncSetAttribute(mamba_scan_tiled_kernel<TO, P, V, FOLD>,                                         \
+            cudaFuncSetAttribute(mamba_scan_tiled_kernel<TO, P, V, FOLD, FAST>,                                   \
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                         \
-        RFX_LAUNCH((mamba_scan_tiled_kernel<TO, P, V, FOLD>), grid, THREADS, smem, st, x, dtpre, dt_bias, bc,     \
-                   ld_bc, b_off, c_off, zsrc, ld_z, z_off, A, Dw, state, (size_t)slot_stride, (size_t)state_off,  \
-                   seq_slot, seq_row0, (TO*)out, channels, N, plan, seg_local, seg_dt, (const float*)seg_begin);  \
+        RFX_LAUNCH((mamba_scan_tiled_kernel<TO, P, V, FOLD, FAST>), grid, THREADS, smem, st, x, dtpre, dt_bias,   \
+                   bc, ld_bc, b_off, c_off, zsrc, ld_z, z_off, A, Dw, state, (size_t)slot_stride,                 \
+                   (size_t)state_off, seq_slot, seq_row0, (TO*)out, channels, N, plan, seg_local, seg_dt,         \
+                   (const float*)seg_begin);                                                                      \
     } while (0)
-#define RFX_TILED_N(TO, V, FOLD)                       \
-    do {                                               \
-        if (npl <= 1) RFX_TILED(TO, 1, V, FOLD);       \
-        else if (npl <= 2) RFX_TILED(TO, 2, V, FOLD);  \
-        else if (npl <= 4) RFX_TILED(TO, 4, V, FOLD);  \
-        else if (npl <= 8) RFX_TILED(TO, 8, V, FOLD);  \
-        else RFX_TILED(TO, 16, V, FOLD);               \
+#define RFX_TILED_N(TO, V, FOLD, FAST)                       \
+    do {                                                     \
+        if (npl <= 1) RFX_TILED(TO, 1, V, FOLD, FAST);       \
+        else if (npl <= 2) RFX_TILED(TO, 2, V, FOLD, FAST);  \
+        else if (npl <= 4) RFX_TILED(TO, 4, V, FOLD, FAST);  \
+        else if (npl <= 8) RFX_TILED(TO, 8, V, FOLD, FAST);  \
+        else RFX_TILED(TO, 16, V, FOLD, FAST);               \
     } while (0)
+        const bool fast = out_dt == RFX_DT_BF16;
         if (G > 1) {
             // the fold writes no rows: one output type serves
-            if (wide) RFX_TILED_N(float, 4, true);
-            else RFX_TILED_N(float, 1, true);
+            if (wide && fast) RFX_TILED_N(float, 4, true, true);
+            else if (wide) RFX_TILED_N(float, 4, true, false);
+            else if (fast) RFX_TILED_N(float, 1, true, true);
+            else RFX_TILED_N(float, 1, true, false);
             const size_t per = (size_t)channels * N;
             RFX_LAUNCH(mamba_scan_carry_kernel, dim3(S, (unsigned)((per + 255) / 256)), 256, 0, st, A,
                        (const float*)state, (size_t)slot_stride, (size_t)state_off, seq_slot,
                        (const float*)seg_local, (const float*)seg_dt, seg_begin, channels, N, G);
         }
         if (out_dt == RFX_DT_F32) {
-            if (wide) RFX_TILED_N(float, 4, false);
-            else RFX_TILED_N(float, 1, false);
+            if (wide) RFX_TILED_N(float, 4, false, false);
+            else RFX_TILED_N(float, 1, false, false);
         } else {
-            if (wide) RFX_TILED_N(__nv_bfloat16, 4, false);
-            else RFX_TILED_N(__nv_bfloat16, 1, false);
+            if (wide) RFX_TILED_N(__nv_bfloat16, 4, false, true);
+            else RFX_TILED_N(__nv_bfloat16, 1, false, true);
         }
 #undef RFX_TILED_N
 #undef RFX_TILED
