@@ -22,7 +22,8 @@ def f32(a):
 
 
 # ------------------------------------------------------------- mechanisms
-@pytest.mark.parametrize("S,W,R", [(1, 64, 3), (2, 100, 5), (3, 328, 70), (4, 4096, 2), (8, 72, 9)])
+@pytest.mark.parametrize("S,W,R", [(1, 64, 3), (2, 100, 5), (3, 328, 70), (4, 4096, 2), (8, 72, 9), (3, 1028, 5),
+                                   (2, 2048, 33), (1, 1024, 32), (8, 1536, 1)])
 @pytest.mark.parametrize("y_dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 def test_streams_write_read_norm_and_sum(S, W, R, y_dtype, out_dtype):
@@ -242,7 +243,7 @@ CUTS = ({0: 197, 1: 9, 2: 81}, {0: 1, 2: 2}, {2: 1}, {0: 2, 2: 14}, {2: 1, 0: 1}
 
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("C,N,taps", [(48, 8, 3), (24, 1, 1), (50, 5, 5), (256, 64, 4), (16, 130, 2), (36, 16, 4),
-                                      (8, 300, 2)])
+                                      (8, 300, 2), (21, 32, 3)])
 @pytest.mark.parametrize("gap", [1, 4])
 def test_filter_silu_and_scan_carried_through_their_state(C, N, taps, out_dtype, gap):
     """Three sequences of unequal lengths in steps of unequal sizes, down to one
