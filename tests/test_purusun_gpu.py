@@ -221,7 +221,7 @@ def test_sigmoid_gate_from_columns_of_a_wider_row_and_squared_relu(a_dtype, z_dt
             (1e-6 if a_dtype == torch.float32 else 8e-3)
 
 
-@pytest.mark.parametrize("R,N,K", [(1, 96, 64), (8, 1000, 328), (33, 256, 2048), (64, 152, 72), (65, 64, 64)])
+@pytest.mark.parametrize("R,N,K", [(1, 96, 64), (8, 1000, 328), (33, 256, 2048), (64, 152, 72), (65, 64, 64), (3, 77, 64), (5, 250, 200)])
 def test_squared_relu_as_the_products_epilogue(R, N, K):
     """A few bfloat16 rows: the activation rides in the product kernel; beyond, apart."""
     g = torch.Generator().manual_seed(R + N)
