@@ -20,7 +20,9 @@
 //    zeros beyond them), so keys and values of different sizes share one
 //    attention kernel.
 //  * rfx_conv_state_update: after the rows have been read, the sequences' new
-//    last taps - 1 inputs.
+//    last taps - 1 inputs.  In a step of one row a sequence rfx_short_conv_act
+//    does this itself (`update`): the thread that read a channel's last inputs
+//    is then their only reader.
 //
 // A row finds its predecessors without a map from rows to sequences: the rows
 // of a sequence are neighbours, so row r - j belongs to it exactly when it has
