@@ -144,6 +144,11 @@ class RunEntry:
     # the run starts from a mix of the stream and the embedding output x0,
     # x <- W [x; x0] with the model's `stream_mix_name` matrix [hidden, 2 hidden]
     mixes_input: bool = False
+    # the run is the first of a pass over a repeated stretch of layers: before it, row
+    # `pass_vector` of the model's `pass_vectors_name` tensor [passes, hidden] is added to
+    # the stream, and with `adds_input` the embedding output x0 as well
+    pass_vector: Optional[int] = None
+    adds_input: bool = False
 
 
 @dataclass
@@ -176,6 +181,10 @@ class ModelSpec:
     # embedding output goes into every copy, the layers' blocks read and rewrite all of
     # them ([rows, streams * hidden] 32-bit), and their sum meets the final norm
     residual_streams: int = 1
+    # the vectors of the runs that start a pass (`RunEntry.pass_vector`), [passes, hidden];
+    # None: the model has none
+    pass_vectors_name: Optional[str] = None
+    pass_vectors: int = 0
 
     def __post_init__(self) -> None:
         if not self.run_order:

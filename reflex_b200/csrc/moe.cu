@@ -3,11 +3,14 @@
 //  * rfx_moe_route: router logits (32-bit, bias added here) -> the `top`
 //    experts with the largest logits (ties: the lower index) and their weights:
 //    the softmax over the chosen logits only (mode 0), or each chosen logit's
-//    sigmoid, not renormalised (mode 1).  One warp a row.
+//    sigmoid, not renormalised (mode 1), or the softmax over all experts with the
+//    chosen ones' scores renormalised by their sum (mode 2); rfx_moe_route_scaled
+//    also multiplies the weights by a constant.  One warp a row.
 //  * rfx_moe_up: act[(r, k), :] = f(W_up[e] (s x[r])) for expert e = ids[r, k];
 //    f = relu squared (act 0) or silu (act 1); act 2 is the gated, clamped form
 //    over W_up[e] = [gate rows | up rows]: g' = min(g, limit), u' = clamp(u,
-//    -limit, limit), g' sigmoid(alpha g') (u' + 1).  `in_scale` (may be null)
+//    -limit, limit), g' sigmoid(alpha g') (u' + 1); act 3 the gated silu over the
+//    same layout, silu(g) u.  `in_scale` (may be null)
 //    gives s per (row, choice): a weight on the expert's input.  One warp an
 //    output element, the row in shared memory.
 //  * rfx_moe_down: y[r, :] = sum_k wts[r, k] W_down[ids[r, k]] act[(r, k), :],
@@ -29,7 +32,7 @@ constexpr int MAX_PER_LANE = 8;  // up to 256 experts
 
 __global__ void moe_route_kernel(const float* __restrict__ logits, int ld, const float* __restrict__ bias,
                                  int* __restrict__ ids, float* __restrict__ wts, int R, int E, int top,
-                                 int mode) {
+                                 int mode, float scale) {
     pdl_prologue();
     const int lane = threadIdx.x & 31;
     const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -69,12 +72,30 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int ld, const
         for (int i = 0; i < MAX_PER_LANE; ++i)
             if (i * 32 + lane == best_e) z[i] = -INFINITY;
     }
+    if (mode == 2) {
+        // scores are the softmax over all experts; the chosen ones' scores over their sum
+        // (+ 1e-20), times `scale`.  z holds -inf where an expert was chosen: the others'
+        // exponentials join the chosen ones' for the softmax's denominator
+        float rest = 0.0f;
+#pragma unroll
+        for (int i = 0; i < MAX_PER_LANE; ++i)
+            if (i * 32 + lane < E && z[i] != -INFINITY) rest += expf(z[i] - zmax);
+        const float total = sum + warp_sum(rest);
+        const float chosen = sum / total + 1e-20f;
+        if (lane < top) {
+            ids[(size_t)r * top + lane] = my_id;
+            wts[(size_t)r * top + lane] = (mine / total) / chosen * scale;
+        }
+        if (lane == 0)
+            for (int k = 32; k < top; ++k) wts[(size_t)r * top + k] = (wts[(size_t)r * top + k] / total) / chosen * scale;
+        return;
+    }
     if (lane < top) {
         ids[(size_t)r * top + lane] = my_id;
-        wts[(size_t)r * top + lane] = mine / sum;
+        wts[(size_t)r * top + lane] = mine / sum * scale;
     }
     if (lane == 0)
-        for (int k = 32; k < top; ++k) wts[(size_t)r * top + k] /= sum;
+        for (int k = 32; k < top; ++k) wts[(size_t)r * top + k] = wts[(size_t)r * top + k] / sum * scale;
 }
 
 // sum_c xs[c] * w[c] over a warp; bfloat16 rows that start on 16 bytes go eight
@@ -140,11 +161,14 @@ moe_up_kernel(const T* __restrict__ x, const T* __restrict__ W, const int* __res
     }
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-    const T* We = W + (size_t)e * (kind == 2 ? 2 : 1) * ff * width;
+    const T* We = W + (size_t)e * (kind >= 2 ? 2 : 1) * ff * width;
     for (int j = blockIdx.y * nwarps + warp; j < ff; j += gridDim.y * nwarps) {
         const T* wrow = We + (size_t)j * width;
         const float dot = warp_dot<T>(xs, wrow, width, lane);
-        if (kind == 2) {
+        if (kind == 3) {  // gated silu over [gate rows | up rows]
+            const float up = warp_dot<T>(xs, wrow + (size_t)ff * width, width, lane);
+            if (lane == 0) st<T>(act, (size_t)pair * ff + j, (dot / (1.0f + expf(-dot))) * up);
+        } else if (kind == 2) {
             const float up = warp_dot<T>(xs, wrow + (size_t)ff * width, width, lane);
             if (lane == 0) {
                 const float g = fminf(dot, limit), u = fminf(fmaxf(up, -limit), limit);
@@ -365,14 +389,22 @@ extern "C" int rfx_moe_combine(const void* yg, int dt, const int* place, const f
 }
 
 // `ld`: floats between two rows of `logits` (>= E: further columns are ignored)
-extern "C" int rfx_moe_route(const float* logits, int ld, const float* bias, int* ids, float* wts, int R, int E,
-                             int top, int mode, void* stream) {
+// mode 2: the softmax over all experts, the chosen ones' scores over their sum (+ 1e-20);
+// `scale` multiplies the weights of every mode
+extern "C" int rfx_moe_route_scaled(const float* logits, int ld, const float* bias, int* ids, float* wts, int R,
+                                    int E, int top, int mode, float scale, void* stream) {
     if (R <= 0) return 0;
-    if (E <= 0 || top <= 0 || top > E || ld < E || (mode != 0 && mode != 1)) return RFX_ERR_BAD_ARG;
+    if (E <= 0 || top <= 0 || top > E || ld < E || mode < 0 || mode > 2) return RFX_ERR_BAD_ARG;
     if (E > 32 * MAX_PER_LANE) return RFX_ERR_UNSUPPORTED;
     RFX_LAUNCH(moe_route_kernel, (R + 3) / 4, 128, 0, (cudaStream_t)stream, logits, ld, bias, ids, wts, R, E, top,
-               mode);
+               mode, scale);
     return 0;
+}
+
+extern "C" int rfx_moe_route(const float* logits, int ld, const float* bias, int* ids, float* wts, int R, int E,
+                             int top, int mode, void* stream) {
+    if (mode != 0 && mode != 1) return RFX_ERR_BAD_ARG;
+    return rfx_moe_route_scaled(logits, ld, bias, ids, wts, R, E, top, mode, 1.0f, stream);
 }
 
 extern "C" int rfx_moe_up(const void* x, const void* W, const int* ids, const float* in_scale, void* act, int dt,

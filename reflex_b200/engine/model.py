@@ -47,6 +47,8 @@ def expected_tensors(spec: ModelSpec) -> Dict[str, Tuple[Tuple[str, ...], Tensor
             out[name] = (("layer", str(li), part, role), info)
     if spec.stream_mix_name is not None:
         out[spec.stream_mix_name] = (("stream_mix",), TensorInfo((spec.hidden_size, 2 * spec.hidden_size), "matrix"))
+    if spec.pass_vectors_name is not None:
+        out[spec.pass_vectors_name] = (("pass_vectors",), TensorInfo((spec.pass_vectors, spec.hidden_size), "bias"))
     out[spec.final_norm_name] = (("final_norm",), NORMS.get(spec.final_norm.kind).tensor_specs(spec.final_norm)["weight"])
     if not spec.tie_word_embeddings:
         out[spec.head_name] = (("head",), TensorInfo((spec.vocab_size, spec.hidden_size), "matrix"))
@@ -66,11 +68,14 @@ class CausalLM:
         self.embedding: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
         self.stream_mix: Optional[torch.Tensor] = None
+        self.pass_vectors: Optional[torch.Tensor] = None
         # a probe for tests and diagnostics: called after every layer run with (index,
         # run, layer, hidden, pending); None in normal use
         self.after_run = None
         if any(r.mixes_input for r in spec.run_order) and spec.stream_mix_name is None:
             raise ValueError("a run mixes its input but the model names no stream-mix matrix")
+        if any(r.pass_vector is not None for r in spec.run_order) and spec.pass_vectors_name is None:
+            raise ValueError("a run adds a pass vector but the model names no tensor of them")
 
     @property
     def capturable(self) -> bool:
@@ -101,6 +106,8 @@ class CausalLM:
                 self.final_norm.bind({"weight": t})
             elif where[0] == "stream_mix":
                 self.stream_mix = t.to(device=self.device, dtype=self.dtype).contiguous()
+            elif where[0] == "pass_vectors":
+                self.pass_vectors = t.to(device=self.device, dtype=torch.float32).contiguous()
             elif where[0] == "embedding_term":
                 per_term.setdefault(int(where[1]), {})[where[2]] = t
             else:
@@ -153,12 +160,14 @@ class CausalLM:
         pending = None
         order = self.spec.run_order
         # the embedding output, for the runs that start from a mix of it and the stream
-        x0 = ops.keep_copy(h) if any(r.mixes_input for r in order) else None
+        x0 = ops.keep_copy(h) if any(r.mixes_input or r.adds_input for r in order) else None
         for i, run in enumerate(order):
             # the norm that will consume this run's result: the next run's first norm, or the final one
             if i + 1 == len(order):
-                next_norm = self.final_norm
-            elif order[i + 1].mixes_input:
+                # a block that would make the last norm for every row leaves it to `logits`
+                next_norm = (None if getattr(self.layers[run.layer], "skips_final_norm_fusion", False)
+                             else self.final_norm)
+            elif order[i + 1].mixes_input or order[i + 1].pass_vector is not None:
                 next_norm = None  # the stream goes through the mix first: no norm to begin here
             else:
                 next_norm = getattr(self.layers[order[i + 1].layer], "fusable_first_norm", None)
@@ -171,6 +180,13 @@ class CausalLM:
                 both = ops.stream_concat(h, pending, x0, self.dtype)
                 h.copy_(ops.linear(both, self.stream_mix, out_dtype=torch.float32))  # the stream's own memory
                 pending = None
+                ops.prof_mark("stream_mix")
+            if run.pass_vector is not None:
+                # the start of a pass: x <- x (+ x0) + the pass's vector, in the stream's own memory
+                if pending is not None and not isinstance(pending, ops.NormedInput):
+                    ops.add_(h, pending)
+                pending = None
+                ops.loop_input_(h, x0 if run.adds_input else None, self.pass_vectors[run.pass_vector])
                 ops.prof_mark("stream_mix")
             ctx = RunContext(batch=batch, writes_cache=run.writes_cache, entry=run.cache)
             kind = cache.has(run.cache)

@@ -2,4 +2,4 @@
 the library knows; a new one is a new module here that calls
 `register_architecture`."""
 
-from . import kegasun, pakarax, purusun, qwen3  # noqa: F401
+from . import kegasun, pakarax, purusun, qwen3, zelinex  # noqa: F401

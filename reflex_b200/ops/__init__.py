@@ -850,18 +850,20 @@ def mlstm_out(num, den, proj, g_off: int, weight, eps: float, heads: int, vdim: 
 
 
 # ------------------------------------------------------- mixture of experts
-MOE_ACTIVATIONS = {"relu2": 0, "silu": 1, "glu_clamped": 2}
+MOE_ACTIVATIONS = {"relu2": 0, "silu": 1, "glu_clamped": 2, "swiglu": 3}
 
 
-MOE_SCORES = {"softmax_top": 0, "sigmoid": 1}
+MOE_SCORES = {"softmax_top": 0, "sigmoid": 1, "softmax_all": 2}
 
 
 def moe_route(logits: torch.Tensor, bias: Optional[torch.Tensor], top: int, experts: Optional[int] = None,
-              scores: str = "softmax_top", col0: int = 0):
+              scores: str = "softmax_top", col0: int = 0, scale: float = 1.0):
     """Router logits float32 [R, experts] (+ bias) -> ids int32 [R, top], the
     experts with the largest logits, and weights float32 [R, top]: the softmax
     over the chosen logits only ("softmax_top"), or each chosen logit's sigmoid
-    as it is ("sigmoid").  With `experts` only that many columns of `logits`,
+    as it is ("sigmoid"), or the softmax over all experts with the chosen ones'
+    scores divided by their sum + 1e-20 ("softmax_all"); `scale` multiplies the
+    weights.  With `experts` only that many columns of `logits`,
     from column `col0` on, are router logits (the rest belongs to the caller: a
     product stacked with others')."""
     R, ld = logits.shape
@@ -870,9 +872,9 @@ def moe_route(logits: torch.Tensor, bias: Optional[torch.Tensor], top: int, expe
         raise InvalidInput("moe_route: the router's columns do not fit into the logits' rows")
     ids = _new((R, top), torch.int32, logits.device)
     wts = _new((R, top), torch.float32, logits.device)
-    st = native.lib().rfx_moe_route(_chk(logits, "logits", torch.float32) + 4 * int(col0), ld,
-                                    _chk(bias, "bias", torch.float32),
-                                    ids.data_ptr(), wts.data_ptr(), R, E, int(top), MOE_SCORES[scores], _stream())
+    st = native.lib().rfx_moe_route_scaled(_chk(logits, "logits", torch.float32) + 4 * int(col0), ld,
+                                           _chk(bias, "bias", torch.float32), ids.data_ptr(), wts.data_ptr(), R, E,
+                                           int(top), MOE_SCORES[scores], float(scale), _stream())
     native.check(st, f"moe_route (experts={E}, top={top})")
     return ids, wts
 
@@ -885,12 +887,12 @@ def moe_experts(x: torch.Tensor, up: torch.Tensor, down: torch.Tensor, ids: torc
     reads its expert's matrices itself: the form for a few rows, and the exact
     one in 32-bit.  "glu_clamped": `up` is [experts, 2 ff, width], an expert's
     gate rows and then its up rows, and act is the clamped gated form with
-    `alpha` and `limit` (`glu_clamped`).  `weight_input`: the weight multiplies
+    `alpha` and `limit` (`glu_clamped`); "swiglu": the same layout, silu(gate) * up.  `weight_input`: the weight multiplies
     the expert's input instead of its output, sum_k down[e] act(up[e] (wts[r, k]
     x[r]))."""
     R, width = x.shape
     E, ff, _w = up.shape
-    gated = activation == "glu_clamped"
+    gated = activation in ("glu_clamped", "swiglu")
     if gated:
         ff //= 2
     top = ids.shape[1]
@@ -930,7 +932,7 @@ def moe_experts_grouped(x: torch.Tensor, up: torch.Tensor, down: torch.Tensor, i
     results are summed in the order of their rank."""
     R, width = x.shape
     E, ff, _w = up.shape
-    gated = activation == "glu_clamped"
+    gated = activation in ("glu_clamped", "swiglu")
     if gated:
         ff //= 2
     top = ids.shape[1]
@@ -940,6 +942,8 @@ def moe_experts_grouped(x: torch.Tensor, up: torch.Tensor, down: torch.Tensor, i
 
     def activate(a):
         """The experts' activation on the up product's rows: in place, or (gated) [n, 2 ff] -> [n, ff]."""
+        if activation == "swiglu":
+            return swiglu(a)
         if gated:
             return glu_clamped(a, alpha, limit)
         native.check(lib.rfx_moe_activation(a.data_ptr(), dt_code(a.dtype), a.numel(),
@@ -1339,6 +1343,181 @@ def mamba_scan(x: torch.Tensor, dtpre: torch.Tensor, dt_bias: Optional[torch.Ten
         _chk(dt_weight, "dt_weight"), dt_code(dt_weight.dtype) if dt_weight is not None else 0,
         dt_weight.shape[1] if dt_weight is not None else 0, int(dt_low_off), _stream())
     native.check(st, f"mamba_scan (channels={C}, states={N})")
+    return out
+
+
+# ------------------------------------------- norms around a sublayer, small companions
+def sandwich_norm(y: torch.Tensor, x: torch.Tensor, post_weight: torch.Tensor, mult: float, eps: float,
+                  next_weight: Optional[torch.Tensor], next_eps: float, out_dtype: torch.dtype):
+    """x <- x + mult * rms_norm(y) * post_weight in place (`y`, `x` float32 [R, H]);
+    with `next_weight` also returns rms_norm(x) * next_weight in `out_dtype`: the
+    norm after one sublayer and the norm before the next in one pass over the row."""
+    R, H = x.shape
+    if tuple(y.shape) != (R, H):
+        raise InvalidInput("sandwich_norm: y and x must have the same shape")
+    out = _new((R, H), out_dtype, x.device) if next_weight is not None else None
+    st = native.lib().rfx_sandwich_norm(
+        _chk(y, "y", torch.float32), _chk(x, "x", torch.float32), _chk(post_weight, "post_weight", torch.float32),
+        float(mult), float(eps), _chk(next_weight, "next_weight", torch.float32), float(next_eps),
+        out.data_ptr() if out is not None else 0, dt_code(out_dtype), R, H, _stream())
+    native.check(st, f"sandwich_norm (H={H})")
+    return out
+
+
+def group_norm_gate(x: torch.Tensor, weight: torch.Tensor, eps: float, groups: int, out_dtype: torch.dtype,
+                    gate: Optional[torch.Tensor] = None, gate_col: int = 0) -> torch.Tensor:
+    """`x` float32 [R, C] in `groups` equal parts, each divided by its own root mean
+    square, times weight[c]; with `gate` (float32 rows, the gate's pre-activations
+    from column `gate_col` on) also times their sigmoid."""
+    R, C = x.shape
+    if C % groups or weight.numel() != C:
+        raise InvalidInput("group_norm_gate: the groups must divide the row and the weight match it")
+    if gate is not None and gate_col + C > gate.shape[1]:
+        raise InvalidInput("group_norm_gate: the gate's columns do not fit into its rows")
+    out = _new((R, C), out_dtype, x.device)
+    st = native.lib().rfx_group_norm_gate(
+        _chk(x, "x", torch.float32), _chk(weight, "weight", torch.float32), float(eps),
+        _chk(gate, "gate", torch.float32), gate.shape[1] if gate is not None else 0, int(gate_col),
+        out.data_ptr(), dt_code(out_dtype), R, C, int(groups), _stream())
+    native.check(st, f"group_norm_gate (C={C}, groups={groups})")
+    return out
+
+
+def xielu_(a: torch.Tensor, alpha_pos: float, alpha_neg: float) -> torch.Tensor:
+    """In place: z > 0: alpha_pos z^2 + z / 2; else alpha_neg (e^z - 1 - z) + z / 2."""
+    st = native.lib().rfx_xielu(_chk(a, "a"), dt_code(a.dtype), a.numel(), float(alpha_pos), float(alpha_neg),
+                                _stream())
+    native.check(st, "xielu")
+    return a
+
+
+def loop_input_(x: torch.Tensor, x0: Optional[torch.Tensor], vec: torch.Tensor) -> torch.Tensor:
+    """x[r] += x0[r] (when given) + vec, float32: the start of a pass over a repeated stretch."""
+    R, H = x.shape
+    if vec.numel() != H or (x0 is not None and x0.shape != x.shape):
+        raise InvalidInput("loop_input: the vector must match a row and x0 the rows")
+    st = native.lib().rfx_loop_input(_chk(x, "x", torch.float32), _chk(x0, "x0", torch.float32),
+                                     _chk(vec, "vec", torch.float32), R, H, _stream())
+    native.check(st, "loop_input")
+    return x
+
+
+def tanh_cols(rows: torch.Tensor, col: int, n: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """tanh of columns [col, col + n) of float32 `rows`, [R, n] in `out_dtype`."""
+    R, ld = rows.shape
+    if col + n > ld:
+        raise InvalidInput("tanh_cols: the columns do not fit into the rows")
+    out = _new((R, n), out_dtype, rows.device)
+    st = native.lib().rfx_tanh_cols(_chk(rows, "rows", torch.float32), ld, int(col), out.data_ptr(),
+                                    dt_code(out_dtype), R, int(n), _stream())
+    native.check(st, "tanh_cols")
+    return out
+
+
+def scaled_sum_(a: torch.Tensor, b: torch.Tensor, sa: float, sb: float) -> torch.Tensor:
+    """a <- sa * a + sb * b, both float32."""
+    if a.shape != b.shape:
+        raise InvalidInput("scaled_sum: shapes differ")
+    st = native.lib().rfx_scaled_sum(_chk(a, "a", torch.float32), _chk(b, "b", torch.float32), float(sa), float(sb),
+                                     a.numel(), _stream())
+    native.check(st, "scaled_sum")
+    return a
+
+
+# ------------------------------------------- attention with sigmoid weights
+def sig_qkv_post(proj: torch.Tensor, col0: int, rotation, row_pos: torch.Tensor, row_slot: torch.Tensor,
+                 k_pages, v_pages, page_table: torch.Tensor, page_size: int, nq: int, nkv: int, dim: int,
+                 vdim: int, writes_cache: bool, out_dtype: torch.dtype) -> torch.Tensor:
+    """Columns [q | k | v] of `proj` from `col0` on (keys `dim` wide, values `vdim`):
+    the rotation of q and k (a half-split `parts.Rotation` or None), q out
+    [R, nq * dim], k and v into their pages at the rows' positions."""
+    R = proj.shape[0]
+    need = nq * dim + (nkv * (dim + vdim) if writes_cache else 0)
+    if col0 + need > proj.shape[1]:
+        raise InvalidInput("sig_qkv_post: the q | k | v columns do not fit into the rows")
+    denom, rot = None, 0
+    if rotation is not None:
+        if rotation.pairing != "half" or rotation.magnitude != 1.0:
+            raise InvalidInput("sig_qkv_post: takes a plain half-split rotation")
+        denom, rot = rotation.denominators, int(rotation.rotary_dim)
+    q = _new((R, nq * dim), out_dtype, proj.device)
+    st = native.lib().rfx_sig_qkv_post(
+        _chk(proj, "proj"), dt_code(proj.dtype), proj.shape[1], int(col0), _chk(denom, "denominators", torch.float32),
+        rot, _chk(row_pos, "row_pos", torch.int32), _chk(row_slot, "row_slot", torch.int32), q.data_ptr(),
+        _chk(k_pages, "k_pages", out_dtype), _chk(v_pages, "v_pages", out_dtype), dt_code(out_dtype),
+        _chk(page_table, "page_table", torch.int32), page_table.shape[1], page_size, R, nq, nkv, dim, vdim,
+        1 if writes_cache else 0, _stream())
+    native.check(st, f"sig_qkv_post (dim={dim}, vdim={vdim})")
+    return q
+
+
+def attention_sigmoid_plain(q, k_pages, v_pages, page_table, page_size, row_pos, row_slot, nq, nkv, dim, vdim,
+                            window, scale, bias) -> torch.Tensor:
+    """out = sum over the visible keys of sigmoid(q . k * scale + bias[head]) v, a
+    warp per (row, head): the 32-bit path and every head size up to 512."""
+    R = q.shape[0]
+    out = _new((R, nq * vdim), q.dtype, q.device)
+    st = native.lib().rfx_attention_sigmoid_plain(
+        _chk(q, "q"), _chk(k_pages, "k_pages", q.dtype), _chk(v_pages, "v_pages", q.dtype), dt_code(q.dtype),
+        _chk(page_table, "page_table", torch.int32), page_table.shape[1], page_size,
+        _chk(row_pos, "row_pos", torch.int32), _chk(row_slot, "row_slot", torch.int32), out.data_ptr(), R, nq, nkv,
+        dim, vdim, int(window or 0), float(scale), _chk(bias, "bias", torch.float32), _stream())
+    native.check(st, f"attention_sigmoid_plain (dim={dim}, vdim={vdim})")
+    return out
+
+
+def attention_sigmoid(q, k_pages, v_pages, page_table, page_size, batch, nq, nkv, dim, vdim, window, scale, bias):
+    """Attention with sigmoid weights for the step's rows; picks the kernel."""
+    return attention_sigmoid_plain(q, k_pages, v_pages, page_table, page_size, batch.row_pos, batch.row_slot,
+                                   nq, nkv, dim, vdim, window, scale, bias)
+
+
+# ------------------------------------------- recurrences with a matrix state a head
+def ssd_scan(xbc: torch.Tensor, proj: torch.Tensor, z_off: int, dt_off: int, dt_bias: torch.Tensor, A: torch.Tensor,
+             D: Optional[torch.Tensor], state: torch.Tensor, state_off: int, batch, heads: int, vdim: int,
+             states: int, groups: int, out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """The state-space recurrence with one decay a head (csrc/ssd.cu): `xbc` float32
+    rows [x | B | C], `proj` float32 rows with z at `z_off` and the step sizes'
+    pre-activations at `dt_off`; `A` float32 [heads], negative; the running state is
+    `state[slot, state_off : state_off + heads * states * vdim]`.  Returns
+    (S^T C + D x) * silu(z), [R, heads * vdim]."""
+    R = xbc.shape[0]
+    inner = heads * vdim
+    if xbc.shape[1] != inner + 2 * groups * states:
+        raise InvalidInput("ssd_scan: xbc must be [rows, heads * vdim + 2 * groups * states]")
+    if z_off + inner > proj.shape[1] or dt_off + heads > proj.shape[1]:
+        raise InvalidInput("ssd_scan: z or dt do not fit into the rows of proj")
+    out = _new((R, inner), out_dtype, xbc.device)
+    st = native.lib().rfx_ssd_scan(
+        _chk(xbc, "xbc", torch.float32), xbc.shape[1], _chk(proj, "proj", torch.float32), proj.shape[1], int(z_off),
+        int(dt_off), _chk(dt_bias, "dt_bias", torch.float32), _chk(A, "A", torch.float32), _chk(D, "D", torch.float32),
+        _chk(state, "state", torch.float32), state.stride(0), int(state_off),
+        _chk(batch.seq_slot, "seq_slot", torch.int32), _chk(batch.seq_row0, "seq_row0", torch.int32),
+        batch.seq_slot.numel(), out.data_ptr(), dt_code(out_dtype), heads, vdim, states, groups, _stream())
+    native.check(st, f"ssd_scan (heads={heads}, vdim={vdim}, states={states})")
+    return out
+
+
+def delta_rule(proj: torch.Tensor, r_off: int, k_off: int, v_off: int, a_off: int, wpre: torch.Tensor,
+               w_bias: torch.Tensor, a_bias: torch.Tensor, rate: float, unit_eps: float, state: torch.Tensor,
+               state_off: int, batch, heads: int, dim: int) -> torch.Tensor:
+    """The generalized delta rule (csrc/delta_rule.cu): `proj` float32 rows with r, k,
+    v and the removal rate's pre-activation at their column offsets (heads * dim
+    each), `wpre` float32 [R, heads * dim] the decay's; the running state is
+    `state[slot, state_off : state_off + heads * dim * dim]`.  Returns S^T r,
+    float32 [R, heads * dim]."""
+    R = proj.shape[0]
+    hd = heads * dim
+    if max(r_off, k_off, v_off, a_off) + hd > proj.shape[1] or tuple(wpre.shape) != (R, hd):
+        raise InvalidInput("delta_rule: the columns do not fit into the rows")
+    out = _new((R, hd), torch.float32, proj.device)
+    st = native.lib().rfx_delta_rule(
+        _chk(proj, "proj", torch.float32), proj.shape[1], int(r_off), int(k_off), int(v_off), int(a_off),
+        _chk(wpre, "wpre", torch.float32), _chk(w_bias, "w_bias", torch.float32), _chk(a_bias, "a_bias", torch.float32),
+        float(rate), float(unit_eps), _chk(state, "state", torch.float32), state.stride(0), int(state_off),
+        _chk(batch.seq_slot, "seq_slot", torch.int32), _chk(batch.seq_row0, "seq_row0", torch.int32),
+        batch.seq_slot.numel(), out.data_ptr(), dt_code(torch.float32), heads, dim, _stream())
+    native.check(st, f"delta_rule (heads={heads}, dim={dim})")
     return out
 
 

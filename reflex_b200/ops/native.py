@@ -108,6 +108,26 @@ _SIGNATURES = {
     "rfx_moe_gather": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "rfx_moe_activation": [c_void_p, c_int, c_longlong, c_int, c_void_p],
     "rfx_moe_combine": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "rfx_moe_route_scaled": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float,
+                             c_void_p],
+    "rfx_sandwich_norm": [c_void_p, c_void_p, c_void_p, c_float, c_float, c_void_p, c_float, c_void_p, c_int, c_int,
+                          c_int, c_void_p],
+    "rfx_group_norm_gate": [c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int,
+                            c_void_p],
+    "rfx_xielu": [c_void_p, c_int, c_longlong, c_float, c_float, c_void_p],
+    "rfx_loop_input": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
+    "rfx_tanh_cols": [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
+    "rfx_scaled_sum": [c_void_p, c_void_p, c_float, c_float, c_longlong, c_void_p],
+    "rfx_sig_qkv_post": [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                         c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "rfx_attention_sigmoid_plain": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p,
+                                    c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
+    "rfx_ssd_scan": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                     c_longlong, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                     c_void_p],
+    "rfx_delta_rule": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_float, c_float,
+                       c_void_p, c_longlong, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
+                       c_void_p],
     "rfx_short_conv": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_longlong,
                        c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
     "rfx_conv_qkv_post": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_void_p,

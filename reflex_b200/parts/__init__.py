@@ -17,3 +17,4 @@ from .registry import (  # noqa: F401
 from . import norm, rope, mlp, attention, block, embedding, latent_attention, mlstm, moe  # noqa: F401,E402
 from . import conv_attention, rglru, pair  # noqa: F401,E402  (registers the parts)
 from . import hyper, selective_scan  # noqa: F401,E402
+from . import sigmoid_attention, ssd, delta_rule  # noqa: F401,E402

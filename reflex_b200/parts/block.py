@@ -2,7 +2,9 @@
 
 "prenorm": h += mixer(norm1(h)); h += ffn(norm2(h))
 (src/model/dense.rs:1441-1484).  "parallel": n = norm1(h); h += mixer(n) + ffn(n),
-one norm that both sublayers read.  The residual stream is 32-bit; each add is
+one norm that both sublayers read.  "sandwich": a norm on both sides of every
+sublayer, h += m * post1(mixer(norm1(h))); h += m * post2(ffn(norm2(h))), m one
+number of the layer.  The residual stream is 32-bit; each add is
 fused into the norm that follows it, so a block hands its last delta on as
 `pending` and the next block's (or the model's final) norm adds it
 (src/model/decode_step.rs:199-210, 293-300).
@@ -196,3 +198,86 @@ class ParallelBlock(PreNormBlock):
             else:
                 delta = ops.add_(delta, self.feed_forward.forward(x))
         return hidden, delta
+
+
+@register_block("sandwich")
+class SandwichBlock(PreNormBlock):
+    """h += m * post1(mixer(norm1(h))); h += m * post2(ffn(norm2(h))): every
+    sublayer's result is normed (weights `post_mixer`, `post_feed_forward` among
+    the spec's `extra_norms`) and multiplied by the spec's `residual_mult` before
+    it joins the 32-bit residual.  The norm after a sublayer and the norm before
+    the next one are one pass over the row (`ops.sandwich_norm`): the block hands
+    the next block its first norm's rows ready (`ReadyRows`) when it is told that
+    norm, and adds into the residual itself, so it never leaves a delta pending."""
+
+    class ReadyRows:
+        """Rows the next block's first norm has already produced."""
+
+        def __init__(self, rows):
+            self.rows = rows
+
+    skips_final_norm_fusion = True  # the model's last norm meets the wanted rows only
+
+    def __init__(self, spec: LayerSpec, dtype: torch.dtype, device):
+        super().__init__(spec, dtype, device)
+        extra = dict(spec.extra_norms)
+        self.dtype = dtype
+        self.mult = float(dict(spec.params).get("residual_mult", 1.0))
+        self.post_mixer = NORMS.get(extra["post_mixer"].kind)(extra["post_mixer"], dtype, device)
+        self.post_feed_forward = (NORMS.get(extra["post_feed_forward"].kind)(extra["post_feed_forward"], dtype, device)
+                                  if self.has_feed_forward else None)
+        for n in (self.mixer_norm, self.feed_forward_norm, self.post_mixer, self.post_feed_forward):
+            if n is not None and (n.spec.kind != "rmsnorm" or n.spec.weight_offset != 0.0):
+                raise ValueError("sandwich block: takes RMS norms with a plain weight")
+
+    @property
+    def fusable_first_norm(self):
+        return self.mixer_norm
+
+    @property
+    def capturable(self) -> bool:
+        return PreNormBlock.capturable.fget(self) and bool(getattr(self.post_mixer, "capturable", False))
+
+    @classmethod
+    def tensor_names(cls, spec: LayerSpec) -> Dict[str, Tuple[str, str, TensorInfo]]:
+        out = PreNormBlock.tensor_names(spec)
+        block_names = names_dict(spec.names)
+        for role, norm in spec.extra_norms:
+            if role == "post_feed_forward" and spec.feed_forward is None:
+                continue
+            info = NORMS.get(norm.kind).tensor_specs(norm)["weight"]
+            out[spec.prefix + block_names.get(role, role + ".weight")] = (role, "weight", info)
+        return out
+
+    def bind(self, by_part: Dict[str, Dict[str, torch.Tensor]]) -> None:
+        super().bind(by_part)
+        self.post_mixer.bind(by_part.get("post_mixer", {}))
+        if self.has_feed_forward:
+            self.post_feed_forward.bind(by_part.get("post_feed_forward", {}))
+
+    def forward(self, hidden: torch.Tensor, pending, ctx, next_norm=None):
+        from .. import ops
+
+        if isinstance(pending, SandwichBlock.ReadyRows):
+            x = pending.rows
+        else:
+            if isinstance(pending, ops.NormedInput):
+                pending = None  # the stream already holds the sum
+            x = self.mixer_norm(hidden, delta=pending)
+            ops.prof_mark("norm")
+        # the norm that follows this block, if it is one this kernel can make
+        nxt = next_norm if isinstance(next_norm, type(self.mixer_norm)) and next_norm.spec.weight_offset == 0.0 else None
+        y = self.mixer.forward(x, ctx)
+        after = self.feed_forward_norm if self.has_feed_forward else nxt
+        x = ops.sandwich_norm(y, hidden, self.post_mixer.weight, self.mult, self.post_mixer.spec.eps,
+                              after.weight if after is not None else None,
+                              after.spec.eps if after is not None else 0.0, self.dtype)
+        ops.prof_mark("norm")
+        if not self.has_feed_forward:
+            return hidden, (SandwichBlock.ReadyRows(x) if x is not None else None)
+        y = self.feed_forward.forward(x)
+        x = ops.sandwich_norm(y, hidden, self.post_feed_forward.weight, self.mult, self.post_feed_forward.spec.eps,
+                              nxt.weight if nxt is not None else None, nxt.spec.eps if nxt is not None else 0.0,
+                              self.dtype)
+        ops.prof_mark("norm")
+        return hidden, (SandwichBlock.ReadyRows(x) if x is not None else None)

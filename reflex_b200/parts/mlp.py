@@ -143,3 +143,45 @@ class SquaredReLU:
         out = ops.linear(act, self.down, out_dtype=torch.float32)
         ops.prof_mark("ffn_down")
         return out
+
+
+@register_feed_forward("xielu")
+class XieluFeedForward:
+    """out = W_down act(W_up x) with act(z) = ap z^2 + z / 2 for z > 0 and
+    an (e^z - 1 - z) + z / 2 otherwise, ap = softplus(p) and an = beta +
+    softplus(q), p and q the two stored numbers of the layer (`act`), beta the
+    spec's parameter.  The two softplus are taken once, when the weights are bound."""
+
+    capturable = True
+
+    def __init__(self, spec: FeedForwardSpec, dtype: torch.dtype, device):
+        self.spec = spec
+        self.dtype = dtype
+        self.device = device
+        self.beta = float(spec.param("beta", 0.5))
+        self.up = self.down = None
+        self.alpha_pos = self.alpha_neg = 0.0
+
+    @classmethod
+    def tensor_specs(cls, spec: FeedForwardSpec) -> Dict[str, TensorInfo]:
+        H, I = spec.hidden_size, spec.intermediate_size
+        return {"up_proj": TensorInfo((I, H), "matrix"), "down_proj": TensorInfo((H, I), "matrix"),
+                "act": TensorInfo((2,), "bias")}
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.up = tensors["up_proj"].to(device=self.device, dtype=self.dtype).contiguous()
+        self.down = tensors["down_proj"].to(device=self.device, dtype=self.dtype).contiguous()
+        p, q = (float(v) for v in tensors["act"].to(device="cpu", dtype=torch.float64).tolist())
+        import math
+
+        def softplus(z: float) -> float:
+            return max(z, 0.0) + math.log1p(math.exp(-abs(z)))
+
+        self.alpha_pos, self.alpha_neg = softplus(p), self.beta + softplus(q)
+
+    def forward(self, x, residual=None):
+        act = ops.xielu_(ops.linear(x, self.up), self.alpha_pos, self.alpha_neg)
+        ops.prof_mark("ffn_gate_up")
+        out = ops.linear(act, self.down, out_dtype=torch.float32)
+        ops.prof_mark("ffn_down")
+        return out

@@ -17,7 +17,12 @@ u = clamp(W_up x, -limit, limit) (its gate and up matrices stacked [experts,
 output is sum_k expert_k(w_k x).  `shared_ff` > 0: a shared expert of that
 width (the same clamped gated form with `shared_limit`) runs for every row and
 is added times sigmoid(w_sg . x), one number a row; its gate's row rides along
-as one more row of the router's matrix.
+as one more row of the router's matrix.  `scores` "softmax_all": the weights are
+the softmax over all experts' logits, the chosen ones' divided by their sum
+(+ 1e-20); `score_scale` multiplies the weights.  `activation` "swiglu": an
+expert is W_down (silu(W_gate x) * (W_up x)).  `shared_kind` "swiglu" (with
+`shared_ff`): the shared expert is that gated silu form and is added as it is,
+with no gate of its own.
 """
 
 from __future__ import annotations
@@ -48,6 +53,8 @@ class MixtureOfExperts:
         self.limit = float(spec.param("limit", 0.0))
         self.shared_ff = int(spec.param("shared_ff", 0) or 0)
         self.shared_limit = float(spec.param("shared_limit", 0.0))
+        self.shared_kind = str(spec.param("shared_kind", "glu_clamped_gated"))
+        self.score_scale = float(spec.param("score_scale", 1.0))
         self.router = self.router_bias = self.up = self.down = None
         self.shared_gate_up = self.shared_down = None
 
@@ -57,7 +64,7 @@ class MixtureOfExperts:
         out = {"router": TensorInfo((E, H), "matrix")}
         if spec.param("router_bias", False):
             out["router_bias"] = TensorInfo((E,), "bias")
-        gated = spec.param("activation") == "glu_clamped"
+        gated = spec.param("activation") in ("glu_clamped", "swiglu")
         for e in range(E):  # role#index: the checkpoint names every expert's tensors
             if gated:
                 out[f"expert_gate#{e}"] = TensorInfo((I, H), "matrix")
@@ -67,6 +74,8 @@ class MixtureOfExperts:
         if S:
             out.update({"shared_gate": TensorInfo((S, H), "matrix"), "shared_up": TensorInfo((S, H), "matrix"),
                         "shared_down": TensorInfo((H, S), "matrix"), "shared_sg": TensorInfo((1, H), "matrix")})
+            if spec.param("shared_kind", "glu_clamped_gated") == "swiglu":
+                del out["shared_sg"]
         return out
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
@@ -76,14 +85,15 @@ class MixtureOfExperts:
         self.router = dev(tensors["router"]).contiguous()
         b = tensors.get("router_bias")
         self.router_bias = None if b is None else b.to(device=self.device, dtype=torch.float32).contiguous()
-        if self.activation == "glu_clamped":  # an expert's gate rows, then its up rows
+        if self.activation in ("glu_clamped", "swiglu"):  # an expert's gate rows, then its up rows
             self.up = torch.stack([torch.cat([dev(tensors[f"expert_gate#{e}"]), dev(tensors[f"expert_up#{e}"])])
                                    for e in range(self.experts)]).contiguous()
         else:
             self.up = torch.stack([dev(tensors[f"expert_up#{e}"]) for e in range(self.experts)]).contiguous()
         self.down = torch.stack([dev(tensors[f"expert_down#{e}"]) for e in range(self.experts)]).contiguous()
         if self.shared_ff:
-            self.router = torch.cat([self.router, dev(tensors["shared_sg"]).reshape(1, -1)]).contiguous()
+            if self.shared_kind != "swiglu":
+                self.router = torch.cat([self.router, dev(tensors["shared_sg"]).reshape(1, -1)]).contiguous()
             g, u = dev(tensors["shared_gate"]), dev(tensors["shared_up"])
             self.shared_gate_up = torch.stack([g, u], dim=1).reshape(2 * g.shape[0], g.shape[1]).contiguous()
             self.shared_down = dev(tensors["shared_down"]).contiguous()
@@ -109,12 +119,17 @@ class MixtureOfExperts:
         else:
             logits, col0 = proj
         ids, wts = ops.moe_route(logits, self.router_bias, self.top, experts=self.experts, scores=self.scores,
-                                 col0=col0)
+                                 col0=col0, scale=self.score_scale)
         ops.prof_mark("moe_router")
         out = ops.moe_experts(x, self.up, self.down, ids, wts, self.activation, self.weight_input, self.alpha,
                               self.limit)
         ops.prof_mark("moe_experts")
-        if self.shared_ff:
+        if self.shared_ff and self.shared_kind == "swiglu":
+            # the shared expert as it is: gate and up woven into one product, added to the experts' sum
+            shared = ops.linear(ops.linear_swiglu(x, self.shared_gate_up), self.shared_down, out_dtype=torch.float32)
+            ops.add_(out, shared)
+            ops.prof_mark("moe_shared")
+        elif self.shared_ff:
             act = ops.linear_glu_clamped(x, self.shared_gate_up, self.alpha, self.shared_limit)
             shared = ops.linear(act, self.shared_down, out_dtype=torch.float32)
             if onto is not None:  # one launch adds both the experts' sum and the gated shared expert

@@ -1,7 +1,9 @@
 """Two mixers side by side on the same input.
 
 out = (norm_l(left(h)) + norm_r(right(h))) / 2, each branch's output over its
-root mean square (over the model width) times a weight of its own.  The two
+root mean square (over the model width) times a weight of its own; or, with the
+spec's `combine` = "scaled_sum", out = left_scale * left(h) + right_scale *
+right(h) with no norm and no tensors of the pair's own.  The two
 branches are registered mixers of any kind, named by the spec's `left` and
 `right` parameters; what they keep in the cache is asked for together (a tuple
 of their specs) and handed to each in turn.  A branch may return `(delta,
@@ -37,7 +39,11 @@ class PairMixer:
         self.spec = spec
         self.dtype = dtype
         self.device = device
-        self.eps = float(spec.param("eps"))
+        self.combine = str(spec.param("combine", "norm_mean"))
+        if self.combine not in ("norm_mean", "scaled_sum"):
+            raise ValueError(f"pair: combine must be norm_mean or scaled_sum, got {self.combine!r}")
+        self.eps = float(spec.param("eps", 0.0) or 0.0)
+        self.scales = (float(spec.param("left_scale", 1.0)), float(spec.param("right_scale", 1.0)))
         self.branches = [MIXERS.get(spec.param(side).kind)(spec.param(side), dtype, device) for side in self.SIDES]
         self.weights = [None, None]
         self.stacked = None   # both branches' first matrices, one above the other
@@ -55,7 +61,8 @@ class PairMixer:
             sub = spec.param(side)
             for role, info in MIXERS.get(sub.kind).tensor_specs(sub).items():
                 out[f"{side}/{role}"] = info
-            out[f"{side}_out"] = TensorInfo((spec.hidden_size,), "norm")
+            if spec.param("combine", "norm_mean") == "norm_mean":
+                out[f"{side}_out"] = TensorInfo((spec.hidden_size,), "norm")
         return out
 
     def cache_spec(self):
@@ -65,7 +72,8 @@ class PairMixer:
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         for i, (side, branch) in enumerate(zip(self.SIDES, self.branches)):
             branch.bind({role[len(side) + 1:]: t for role, t in tensors.items() if role.startswith(side + "/")})
-            self.weights[i] = tensors[f"{side}_out"].to(device=self.device, dtype=torch.float32).contiguous()
+            if self.combine == "norm_mean":
+                self.weights[i] = tensors[f"{side}_out"].to(device=self.device, dtype=torch.float32).contiguous()
         if all(hasattr(b, "input_weight") and hasattr(b, "adopt_input_weight") for b in self.branches):
             parts = [b.input_weight() for b in self.branches]
             if all(p is not None and p.dtype == parts[0].dtype and p.shape[1] == parts[0].shape[1] for p in parts):
@@ -111,6 +119,12 @@ class PairMixer:
                  else branch.forward(x, sub, proj=(proj, col0 + self.first_col[bi])))
             outs.append(r if isinstance(r, tuple) else (r, None))
         (a, a_bias), (b, b_bias) = outs
+        if self.combine == "scaled_sum":
+            if a_bias is not None or b_bias is not None:
+                raise ValueError("pair: the scaled sum takes branches without a deferred bias")
+            out = ops.scaled_sum_(a, b, self.scales[0], self.scales[1])
+            ops.prof_mark("pair_out")
+            return out
         if b_bias is not None:  # the kernel takes one bias: give it the branch that has one
             if a_bias is not None:
                 b = b + b_bias

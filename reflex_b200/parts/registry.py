@@ -47,6 +47,15 @@ class TensorInfo:
     # "coef":   mixing coefficients of several residual streams, kept 32-bit, drawn U(0.2, 0.8)
     role: str
     optional: bool = False
+    # a dimension given as -1 is taken from the checkpoint (a low rank that only the
+    # tensor's shape tells); `free` is the size a writer of random weights gives it
+    free: int = 0
+
+    def concrete_shape(self) -> Tuple[int, ...]:
+        return tuple(self.free if n == -1 else n for n in self.shape)
+
+    def fits(self, shape) -> bool:
+        return len(shape) == len(self.shape) and all(w == -1 or int(w) == int(h) for w, h in zip(self.shape, shape))
 
 
 @dataclass(frozen=True)

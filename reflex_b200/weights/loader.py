@@ -52,7 +52,7 @@ def check_names_and_shapes(spec: ModelSpec, ckpt) -> None:
     for n, (_, info) in exp.items():
         if n in have:
             dtype, shape = ckpt.info(n)
-            if tuple(shape) != tuple(info.shape):
+            if not info.fits(shape):
                 wrong.append(f"{n}: expected {list(info.shape)}, found {list(shape)}")
             elif not (dtype.is_floating_point):
                 wrong.append(f"{n}: expected a floating-point tensor, found {dtype}")

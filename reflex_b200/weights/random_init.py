@@ -123,7 +123,7 @@ def random_tensors(spec: ModelSpec, seed: int, dtype: torch.dtype, device="cpu")
     from ..engine.model import expected_tensors
 
     for name, (_where, info) in expected_tensors(spec).items():
-        yield name, draw(name, info.shape, info.role, seed, device, dtype)
+        yield name, draw(name, info.concrete_shape(), info.role, seed, device, dtype)
 
 
 def write_random_model(config: Dict[str, Any], seed: int, out_dir: str, dtype: str = "bfloat16") -> str:
@@ -153,7 +153,7 @@ def random_model_on_device(config: Dict[str, Any], seed: int, dtype: torch.dtype
     store = torch.bfloat16 if dtype == torch.bfloat16 else torch.float32
     tensors = {}
     for name, (_where, info) in expected_tensors(spec).items():
-        tensors[name] = draw(name, info.shape, info.role, seed, device,
+        tensors[name] = draw(name, info.concrete_shape(), info.role, seed, device,
                              torch.float32 if info.role in SMALL_ROLES else store)
     model.bind(tensors)
     return model
