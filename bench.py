@@ -318,6 +318,30 @@ def purusun_config(z):
             "streams": 4, "layers": layers}
 
 
+def zelinex_config(z):
+    """Zelinex at the sizes of `z`: layers of a sigmoid-weight attention (a quarter
+    as many key/value heads, half of each head rotated, the window of the models
+    beside it) beside a state-space recurrence of the model's width (heads of 64
+    channels, 128 states, two groups, four taps) with a dense feed-forward, in turn
+    with layers of a delta rule of the model's width (heads of 64) with experts and a
+    shared expert; all layers form one pass of the loop, so that the number of layer
+    runs equals the models beside it."""
+    pair = {"type": "parallel",
+            "mixer": {"left": {"heads": z["heads"], "kv_heads": max(1, z["heads"] // 4), "dim": z["dim"],
+                               "vdim": z["dim"], "scale": z["dim"] ** -0.5,
+                               "rot": {"base": 1000000.0, "dims": z["dim"] // 2}, "mask": {"size": z["window"]}},
+                      "right": {"heads": z["width"] // 64, "vdim": 64, "state": 128, "groups": 2, "conv": 4,
+                                "norm_groups": 2},
+                      "left_scale": 0.6, "right_scale": 0.5}}
+    delta = {"type": "general_delta", "mixer": {"heads": z["width"] // 64, "dim": 64}}
+    dense = {"kind": "dense", "ff": z["ff"]}
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]},
+           "router": {"experts": z["experts"], "top": z["top"], "scale": 1.5}, "shared": {"ff": z["expert_ff"]}}
+    layers = [dict((pair, delta)[i % 2], mlp=(dense, moe)[i % 2]) for i in range(z["layers"])]
+    return {"architecture": "Zelinex", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5},
+            "residual_mult": 0.7, "loop": {"start": 0, "stop": z["layers"], "times": 1}, "layers": layers}
+
+
 def qwen3_config_like(z):
     cfg = dict(QWEN3_8B)
     cfg.update({"num_hidden_layers": z["layers"], "hidden_size": z["width"], "num_attention_heads": z["heads"],
@@ -330,7 +354,8 @@ def qwen3_config_like(z):
 def design_comparison(args) -> int:
     """Prefill and decode throughput of a design (`--design`) beside Qwen3 at
     equal sizes (and, for Pakarax, beside Kegasun too: the model with a
-    recurrence and experts), with every phase's time in a prefill and in a
+    recurrence and experts; for Zelinex beside Pakarax: the model with two mixers
+    side by side, experts and a loop), with every phase's time in a prefill and in a
     decode step."""
     import torch
 
@@ -342,8 +367,10 @@ def design_comparison(args) -> int:
     torch.cuda.set_device(0)
     T, B, P, steps = PREFILL_TOKENS, args.batch, PROMPT, max(16, min(args.steps, 64))
     mine = args.design
-    beside = [("qwen3", qwen3_config_like)] + ([("kegasun", kegasun_config)] if mine == "pakarax" else [])
-    mine_config = {"kegasun": kegasun_config, "pakarax": pakarax_config, "purusun": purusun_config}[mine]
+    beside = [("qwen3", qwen3_config_like)] + ([("kegasun", kegasun_config)] if mine == "pakarax" else []) \
+        + ([("pakarax", pakarax_config)] if mine == "zelinex" else [])
+    mine_config = {"kegasun": kegasun_config, "pakarax": pakarax_config, "purusun": purusun_config,
+                   "zelinex": zelinex_config}[mine]
     out = {"metric": f"prefill and decode tokens/s, {mine} beside " + " and ".join(n for n, _ in beside)
                      + " at equal sizes", "unit": "tokens/s",
            "dtype": "bf16", "data": "synthetic: seeded uniform token ids, random-init weights",
@@ -468,7 +495,7 @@ def main() -> int:
                     help="workloads beside the headline: 14b and 32b add their points (default: all)")
     ap.add_argument("--prompt", type=int, default=PROMPT, help="prompt tokens before the decode steps")
     ap.add_argument("--context", type=int, default=CONTEXT, help="cache positions per sequence")
-    ap.add_argument("--design", default="", choices=["", "kegasun", "pakarax", "purusun"],
+    ap.add_argument("--design", default="", choices=["", "kegasun", "pakarax", "purusun", "zelinex"],
                     help="instead of the headline: this design beside Qwen3 at equal sizes (prefill, decode, phases)")
     ap.add_argument("--sizes", default="w1024,w2048,w4096", help="with --design: which of the sizes " +
                     ", ".join(sorted(DESIGN_SIZES)))

@@ -1466,8 +1466,32 @@ def attention_sigmoid_plain(q, k_pages, v_pages, page_table, page_size, row_pos,
     return out
 
 
+def attention_sigmoid_mma(q, k_pages, v_pages, page_table, page_size, seq_slot, seq_start, seq_new, seq_row0,
+                          max_new: int, nq, nkv, dim, vdim, window, scale, bias) -> torch.Tensor:
+    """The bfloat16 tensor-core form (csrc/sigmoid_attention_mma.cu) for a packed batch of
+    sequences that each bring one or more rows: key sizes in steps of 8 up to 256, value
+    sizes up to 128, up to 128 query heads a key head."""
+    _chk(q, "q", torch.bfloat16)
+    R = q.shape[0]
+    out = _new((R, nq * vdim), q.dtype, q.device)
+    st = native.lib().rfx_attention_sigmoid_mma(
+        q.data_ptr(), _chk(k_pages, "k_pages", torch.bfloat16), _chk(v_pages, "v_pages", torch.bfloat16),
+        _chk(page_table, "page_table", torch.int32), page_table.shape[1], page_size,
+        _chk(seq_slot, "seq_slot", torch.int32), _chk(seq_start, "seq_start", torch.int32),
+        _chk(seq_new, "seq_new", torch.int32), _chk(seq_row0, "seq_row0", torch.int32), out.data_ptr(),
+        seq_slot.numel(), int(max_new), nq, nkv, dim, vdim, int(window or 0), float(scale),
+        _chk(bias, "bias", torch.float32), _stream())
+    native.check(st, f"attention_sigmoid_mma (dim={dim}, vdim={vdim})")
+    return out
+
+
 def attention_sigmoid(q, k_pages, v_pages, page_table, page_size, batch, nq, nkv, dim, vdim, window, scale, bias):
     """Attention with sigmoid weights for the step's rows; picks the kernel."""
+    if (q.dtype == torch.bfloat16 and dim % 8 == 0 and vdim % 8 == 0 and dim <= 256 and vdim <= 128
+            and nq // nkv <= 128 and page_size == 64):
+        return attention_sigmoid_mma(q, k_pages, v_pages, page_table, page_size, batch.seq_slot, batch.seq_start,
+                                     batch.seq_new, batch.seq_row0, batch.max_new, nq, nkv, dim, vdim, window,
+                                     scale, bias)
     return attention_sigmoid_plain(q, k_pages, v_pages, page_table, page_size, batch.row_pos, batch.row_slot,
                                    nq, nkv, dim, vdim, window, scale, bias)
 
