@@ -13,7 +13,9 @@
 // channel), carried from step to step.  `rate` and `unit_eps` are the caller's
 // constants.  Everything is 32-bit.
 //
-// A block owns (sequence, head, slice of CW value channels) and walks the
+// Two forms.  The one below the general one takes head sizes that are a multiple
+// of four (see there).  The general one:
+// a block owns (sequence, head, slice of CW value channels) and walks the
 // sequence's rows in order with its columns of S in shared memory.  Thread
 // (g, j) takes the key channels i = g, g + KG, ... of column j; the KG partial
 // sums of u^T S and of S^T r meet in shared memory in index order.
@@ -103,6 +105,146 @@ delta_rule_kernel(const float* __restrict__ proj, int ld, int r_off, int k_off, 
     }
 }
 
+
+// ---- the form for head sizes that are a multiple of four, up to 256 ------------
+// A block owns (sequence, head, some of the value columns) and walks the rows in
+// tiles of TT: all its threads first stage a tile (k, a, w, r and v of its rows into
+// shared memory, 16 bytes a load, then a warp a row: the unit key's norm by the lanes'
+// butterfly, u and a * u), then each warp walks the tile's rows on its own four
+// columns with no further barrier: lane (g, c) holds the key channels 4 (g + 8 m) ..
+// + 3 of column c in registers (NC groups of four, read from the tile 16 bytes at a
+// time), the eight partial sums of u^T S and of S^T r meet by shuffles.  The state
+// lies [heads][value column][key channel].  Which block and warp walks a column
+// changes nothing of its arithmetic.
+template <int NC, typename TO>
+__global__ void __launch_bounds__(512)
+delta_rule_warp_kernel(const float* __restrict__ proj, int ld, int r_off, int k_off, int v_off, int a_off,
+                       const float* __restrict__ wpre, const float* __restrict__ w_bias,
+                       const float* __restrict__ a_bias, float rate, float unit_eps, float* __restrict__ state,
+                       long long state_stride, long long state_off, const int* __restrict__ seq_slot,
+                       const int* __restrict__ seq_row0, TO* __restrict__ out, int heads, int d, int cols, int TT) {
+    extern __shared__ __align__(16) float sm[];  // [TT][6][d]: k, u, a * u, w, r, v
+    pdl_prologue();
+    const int seq = blockIdx.x, h = blockIdx.y, c_first = blockIdx.z * cols;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    const int g = lane >> 2, col = c_first + warp * 4 + (lane & 3);
+    const int row0 = seq_row0[seq], row1 = seq_row0[seq + 1];
+    const int hd = heads * d, d4 = d / 4;
+    float* Sg = state + (size_t)seq_slot[seq] * state_stride + state_off + ((size_t)h * d + col) * d;
+    float S[NC][4];
+#pragma unroll
+    for (int m = 0; m < NC; ++m)
+#pragma unroll
+        for (int q = 0; q < 4; ++q) S[m][q] = g + 8 * m < d4 ? Sg[4 * (g + 8 * m) + q] : 0.0f;
+    const float4* ab4 = reinterpret_cast<const float4*>(a_bias + h * d);
+    const float4* wb4 = reinterpret_cast<const float4*>(w_bias + h * d);
+    for (int t0 = row0; t0 < row1; t0 += TT) {
+        const int nt = min(TT, row1 - t0);
+        __syncthreads();  // the tile before has been walked by every warp
+        // four neighbouring elements by whichever thread comes to them: all their loads
+        // first, then the arithmetic, so that many rows' loads are in flight together
+#pragma unroll 2
+        for (int e = threadIdx.x; e < nt * d4; e += blockDim.x) {
+            const int t = e / d4, c = e - t * d4;
+            const float* pr = proj + (size_t)(t0 + t) * ld + h * d;
+            const float4 kv = reinterpret_cast<const float4*>(pr + k_off)[c];
+            const float4 ap = reinterpret_cast<const float4*>(pr + a_off)[c];
+            const float4 rv = reinterpret_cast<const float4*>(pr + r_off)[c];
+            const float4 vv = reinterpret_cast<const float4*>(pr + v_off)[c];
+            const float4 wv = reinterpret_cast<const float4*>(wpre + (size_t)(t0 + t) * hd + h * d)[c];
+            const float4 ab = ab4[c], wb = wb4[c];
+            float4* tile = reinterpret_cast<float4*>(sm + (size_t)t * 6 * d);
+            tile[c] = kv;
+            tile[2 * d4 + c] = make_float4(sigmoid_f(ap.x + ab.x), sigmoid_f(ap.y + ab.y), sigmoid_f(ap.z + ab.z),
+                                           sigmoid_f(ap.w + ab.w));  // a; times u below
+            tile[3 * d4 + c] = make_float4(expf(-rate * sigmoid_f(wv.x + wb.x)), expf(-rate * sigmoid_f(wv.y + wb.y)),
+                                           expf(-rate * sigmoid_f(wv.z + wb.z)), expf(-rate * sigmoid_f(wv.w + wb.w)));
+            tile[4 * d4 + c] = rv;
+            tile[5 * d4 + c] = vv;
+        }
+        __syncthreads();
+        // a warp a row: the unit key by the lanes' butterfly
+        for (int t = warp; t < nt; t += nwarps) {
+            float* tile = sm + (size_t)t * 6 * d;
+            float kk = 0.0f;
+            for (int i = lane; i < d; i += 32) kk = fmaf(tile[i], tile[i], kk);
+            const float inv = 1.0f / sqrtf(warp_sum(kk) + unit_eps);
+            for (int i = lane; i < d; i += 32) {
+                const float u = tile[i] * inv;
+                tile[d + i] = u;
+                tile[2 * d + i] *= u;
+            }
+        }
+        __syncthreads();
+        for (int t = 0; t < nt; ++t) {
+            const float4* tile = reinterpret_cast<const float4*>(sm + (size_t)t * 6 * d);
+            float acc = 0.0f, acc1 = 0.0f;
+#pragma unroll
+            for (int m = 0; m < NC; ++m) {
+                const int c = g + 8 * m;
+                if (c < d4) {
+                    const float4 u = tile[d4 + c];
+                    acc = fmaf(u.x, S[m][0], fmaf(u.y, S[m][1], acc));
+                    acc1 = fmaf(u.z, S[m][2], fmaf(u.w, S[m][3], acc1));
+                }
+            }
+            acc += acc1;
+            acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+            acc += __shfl_xor_sync(0xffffffffu, acc, 8);
+            acc += __shfl_xor_sync(0xffffffffu, acc, 16);
+            const float vj = reinterpret_cast<const float*>(tile)[5 * d + col];
+            float o = 0.0f, o1 = 0.0f;
+#pragma unroll
+            for (int m = 0; m < NC; ++m) {
+                const int c = g + 8 * m;
+                if (c < d4) {
+                    const float4 k = tile[c], au = tile[2 * d4 + c], w = tile[3 * d4 + c], r = tile[4 * d4 + c];
+                    S[m][0] = fmaf(k.x, vj, fmaf(w.x, S[m][0], -au.x * acc));
+                    S[m][1] = fmaf(k.y, vj, fmaf(w.y, S[m][1], -au.y * acc));
+                    S[m][2] = fmaf(k.z, vj, fmaf(w.z, S[m][2], -au.z * acc));
+                    S[m][3] = fmaf(k.w, vj, fmaf(w.w, S[m][3], -au.w * acc));
+                    o = fmaf(S[m][0], r.x, fmaf(S[m][1], r.y, o));
+                    o1 = fmaf(S[m][2], r.z, fmaf(S[m][3], r.w, o1));
+                }
+            }
+            o += o1;
+            o += __shfl_xor_sync(0xffffffffu, o, 4);
+            o += __shfl_xor_sync(0xffffffffu, o, 8);
+            o += __shfl_xor_sync(0xffffffffu, o, 16);
+            if (g == 0) st<TO>(out, (size_t)(t0 + t) * hd + h * d + col, o);
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < NC; ++m)
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+            if (g + 8 * m < d4) Sg[4 * (g + 8 * m) + q] = S[m][q];
+}
+
+template <int NC, typename TO>
+int launch_warp(const float* proj, int ld, int r_off, int k_off, int v_off, int a_off, const float* wpre,
+                const float* w_bias, const float* a_bias, float rate, float unit_eps, float* state,
+                long long state_stride, long long state_off, const int* seq_slot, const int* seq_row0, int n_seq,
+                void* out, int heads, int d, cudaStream_t s) {
+    // value columns a block owns (four a warp): fewer while the blocks do not fill the SMs
+    int cols = d <= 64 ? d : 64;
+    if (d % cols) return RFX_ERR_UNSUPPORTED;
+    while (cols % 8 == 0 && cols > 16 && (long long)n_seq * heads * (d / cols) < sm_count()) cols /= 2;
+    int TT = (48 * 1024) / (6 * d * (int)sizeof(float));
+    if (TT > 32) TT = 32;
+    if (TT < 1) TT = 1;
+    const size_t smem = (size_t)TT * 6 * d * sizeof(float);
+    auto kernel = delta_rule_warp_kernel<NC, TO>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    dim3 grid(n_seq, heads, d / cols);
+    RFX_LAUNCH(kernel, grid, (cols / 4) * 32, smem, s, proj, ld, r_off, k_off, v_off, a_off, wpre, w_bias, a_bias,
+               rate, unit_eps, state, state_stride, state_off, seq_slot, seq_row0, (TO*)out, heads, d, cols, TT);
+    return 0;
+}
+
 }  // namespace
 
 extern "C" int rfx_delta_rule(const float* proj, int ld, int r_off, int k_off, int v_off, int a_off,
@@ -112,6 +254,20 @@ extern "C" int rfx_delta_rule(const float* proj, int ld, int r_off, int k_off, i
                               int heads, int d, void* stream) {
     if (n_seq <= 0) return 0;
     if (heads <= 0 || d <= 0) return RFX_ERR_BAD_ARG;
+    const bool aligned = ((ld | r_off | k_off | v_off | a_off) & 3) == 0 &&
+                         ((reinterpret_cast<uintptr_t>(proj) | reinterpret_cast<uintptr_t>(wpre) |
+                           reinterpret_cast<uintptr_t>(w_bias) | reinterpret_cast<uintptr_t>(a_bias)) & 15) == 0;
+    if (d % 4 == 0 && d <= 256 && out_dt == RFX_DT_F32 && aligned) {
+#define RFX_WARP(N)                                                                                          \
+    return launch_warp<N, float>(proj, ld, r_off, k_off, v_off, a_off, wpre, w_bias, a_bias, rate, unit_eps, \
+                                 state, state_stride, state_off, seq_slot, seq_row0, n_seq, out, heads, d,   \
+                                 (cudaStream_t)stream)
+        if (d <= 32) RFX_WARP(1);
+        if (d <= 64) RFX_WARP(2);
+        if (d <= 128) RFX_WARP(4);
+        RFX_WARP(8);
+#undef RFX_WARP
+    }
     // the slice of value channels a block owns, fixed by d alone
     int CW = d;
     while (CW > 32 && CW % 2 == 0) CW /= 2;

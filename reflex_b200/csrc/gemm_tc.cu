@@ -125,11 +125,16 @@ __device__ __forceinline__ float gated_act(float g, float u, const Fuse& f) {
 
 // The plain epilogue's last step: EPI 5 squares the rectified result, y = max(x W^T, 0)^2
 // (an ungated feed-forward's activation), a template instance of its own beside EPI 0.
+// EPI 6: y = xielu(x W^T) with the two coefficients in `act_alpha` (positive branch) and
+// `act_limit` (negative branch): z > 0: ap z^2 + z / 2; else an (e^z - 1 - z) + z / 2.
 template <int EPI>
-__device__ __forceinline__ float plain_out(float a) {
+__device__ __forceinline__ float plain_out(float a, const Fuse& f) {
     if constexpr (EPI == 5) {
         const float m = fmaxf(a, 0.0f);
         return m * m;
+    }
+    if constexpr (EPI == 6) {
+        return a > 0.0f ? fmaf(f.act_alpha * a, a, 0.5f * a) : fmaf(f.act_limit, expm1f(a) - a, 0.5f * a);
     }
     return a;
 }
@@ -333,7 +338,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const int nkb = max(0, min(num_kb, kb0 + per) - kb0);
     // rows of the tile that each rank of a K-split cluster finishes
     constexpr bool GATED = EPI == 1 || EPI == 4;  // rows alternate gate, up; the epilogue writes their activation
-    constexpr bool PLAIN = EPI == 0 || EPI == 5;  // y = x W^T, EPI 5: y = max(x W^T, 0)^2
+    constexpr bool PLAIN = EPI == 0 || EPI == 5 || EPI == 6;  // y = x W^T, EPI 5: y = max(x W^T, 0)^2, EPI 6: xielu of it
     const int mw = GATED ? ((((bm + ksplit - 1) / ksplit) + 1) & ~1) : (bm + ksplit - 1) / ksplit;
 
     if (threadIdx.x == 0) {
@@ -572,7 +577,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                             const float f = rstd_s[rr];
                             acc.x *= f, acc.y *= f, acc.z *= f, acc.w *= f;
                         }
-                        if (EPI == 5) acc = make_float4(plain_out<5>(acc.x), plain_out<5>(acc.y), plain_out<5>(acc.z), plain_out<5>(acc.w));
+                        if (EPI == 5 || EPI == 6) acc = make_float4(plain_out<EPI>(acc.x, fuse), plain_out<EPI>(acc.y, fuse), plain_out<EPI>(acc.z, fuse), plain_out<EPI>(acc.w, fuse));
                         if (!dry) store4(y + (size_t)r * N + n, acc);
                     }
                 } else if (quads && GATED) {
@@ -656,7 +661,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         for (int p = 0; p < ksplit; ++p) acc += recv[((size_t)p * BN + rr) * mw + ml1];
                         if (PRO) acc *= rstd_s[rr];
                         const int r = r0 + rr;
-                        if (r < R && n0 + mm < N && !dry) rfx::st<TO>(y, (size_t)r * N + n0 + mm, plain_out<EPI>(acc));
+                        if (r < R && n0 + mm < N && !dry) rfx::st<TO>(y, (size_t)r * N + n0 + mm, plain_out<EPI>(acc, fuse));
                     }
                 } else if (GATED) {
                     const int pw = mw / 2;
@@ -746,7 +751,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                             float a = v[j];
                             if (PRO) a *= rstd_s[rr];
                             if (PLAIN) {
-                                if (r < R && m < bm && n < N && !dry) rfx::st<TO>(y, (size_t)r * N + n, plain_out<EPI>(a));
+                                if (r < R && m < bm && n < N && !dry) rfx::st<TO>(y, (size_t)r * N + n, plain_out<EPI>(a, fuse));
                             } else {
                                 float hv1 = 0.0f;
                                 if (r < R && m < bm && n < N && !dry) {
@@ -1030,6 +1035,21 @@ extern "C" int rfx_gemm_bf16_tc_relu2(const void* x, const void* W, void* y, int
     Fuse f{};
     if (y_dt == RFX_DT_BF16)
         return dispatch<__nv_bfloat16, 5, false>(x, W, y, R, N, K, ksplit, f, nullptr, err, (cudaStream_t)stream);
+    return RFX_ERR_UNSUPPORTED;
+}
+
+// y [R, N] = xielu(x W^T) as the product's epilogue, for a decode-sized batch (R <= 64):
+// z > 0: ap z^2 + z / 2; else an (e^z - 1 - z) + z / 2.
+extern "C" int rfx_gemm_bf16_tc_xielu(const void* x, const void* W, void* y, int y_dt, int R, int N, int K,
+                                      int ksplit, float ap, float an, int* err, void* stream) {
+    if (R <= 0 || N <= 0) return 0;
+    if (int c = check_common(x, W, R, N, K)) return c;
+    if (R > 64) return RFX_ERR_UNSUPPORTED;
+    Fuse f{};
+    f.act_alpha = ap;
+    f.act_limit = an;
+    if (y_dt == RFX_DT_BF16)
+        return dispatch<__nv_bfloat16, 6, false>(x, W, y, R, N, K, ksplit, f, nullptr, err, (cudaStream_t)stream);
     return RFX_ERR_UNSUPPORTED;
 }
 

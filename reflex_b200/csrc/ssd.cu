@@ -13,7 +13,9 @@
 // is `state[slot * stride + off ...]`, [heads][N][P] float32, carried from step to
 // step.  Everything is 32-bit.
 //
-// A block owns (sequence, head, slice of the P channels) and walks the
+// Two forms.  The one below the general one takes channel and state counts that are
+// multiples of four, up to 256 states (see there).  The general one:
+// a block owns (sequence, head, slice of the P channels) and walks the
 // sequence's rows in order; its part of S lives in shared memory; thread
 // (k, p) takes the states n = k, k + KG, ... of channel p, and the KG partial
 // sums of y meet in shared memory in index order, so a row's result does not
@@ -86,6 +88,130 @@ ssd_scan_kernel(const float* __restrict__ xbc, int ldx, const float* __restrict_
     }
 }
 
+
+// ---- the form for channel and state counts that are multiples of four -------------
+// A block owns (sequence, head, some of the channels) and walks the rows in tiles of
+// TT: all its threads first stage a tile (B, C, x and z of its rows, 16 bytes a load,
+// their step sizes and decays into shared memory), then each warp walks the tile's
+// rows on its own four channels with no further barrier: lane (g, c) holds the states
+// 4 (g + 8 m) .. + 3 of channel c in registers (NC groups of four, B and C read from
+// the tile 16 bytes at a time), the eight partial sums of y meet by shuffles.  The
+// state lies [heads][channel][state].  Which block and warp walks a channel changes
+// nothing of its arithmetic.
+template <int NC, typename TO>
+__global__ void __launch_bounds__(512)
+ssd_scan_warp_kernel(const float* __restrict__ xbc, int ldx, const float* __restrict__ proj, int ldp, int z_off,
+                     int dt_off, const float* __restrict__ dt_bias, const float* __restrict__ A,
+                     const float* __restrict__ D, float* __restrict__ state, long long state_stride,
+                     long long state_off, const int* __restrict__ seq_slot, const int* __restrict__ seq_row0,
+                     TO* __restrict__ out, int heads, int P, int N, int groups, int cols, int TT) {
+    extern __shared__ __align__(16) float sm[];  // [TT][2 N + 2 cols + 4]: B, C, x, z, dt, decay
+    pdl_prologue();
+    const int seq = blockIdx.x, h = blockIdx.y, c_first = blockIdx.z * cols;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, cl = warp * 4 + (lane & 3), col = c_first + cl;
+    const int grp = h / (heads / groups);
+    const int inner = heads * P, N4 = N / 4, c4 = cols / 4;
+    const int row0 = seq_row0[seq], row1 = seq_row0[seq + 1];
+    const int stride = 2 * N + 2 * cols + 4, stride4 = stride / 4;
+    float* Sg = state + (size_t)seq_slot[seq] * state_stride + state_off + ((size_t)h * P + col) * N;
+    float S[NC][4];
+#pragma unroll
+    for (int m = 0; m < NC; ++m)
+#pragma unroll
+        for (int q = 0; q < 4; ++q) S[m][q] = g + 8 * m < N4 ? Sg[4 * (g + 8 * m) + q] : 0.0f;
+    const float a = A[h], dcoef = D ? D[h] : 0.0f, bias = dt_bias ? dt_bias[h] : 0.0f;
+    float4* sm4 = reinterpret_cast<float4*>(sm);
+    for (int t0 = row0; t0 < row1; t0 += TT) {
+        const int nt = min(TT, row1 - t0);
+        __syncthreads();  // the tile before has been walked by every warp
+        const float* xr0 = xbc + (size_t)t0 * ldx;
+        const float* pr0 = proj + (size_t)t0 * ldp;
+#pragma unroll 4
+        for (int e = threadIdx.x; e < nt * 2 * N4; e += blockDim.x) {  // B and C
+            const int t = e / (2 * N4), c = e - t * 2 * N4;
+            const int src = c < N4 ? inner + grp * N + 4 * c : inner + groups * N + grp * N + 4 * (c - N4);
+            sm4[(size_t)t * stride4 + c] = *reinterpret_cast<const float4*>(xr0 + (size_t)t * ldx + src);
+        }
+#pragma unroll 4
+        for (int e = threadIdx.x; e < nt * c4; e += blockDim.x) {  // x and z
+            const int t = e / c4, c = e - t * c4;
+            const float4 xv = *reinterpret_cast<const float4*>(xr0 + (size_t)t * ldx + h * P + c_first + 4 * c);
+            const float4 zv = *reinterpret_cast<const float4*>(pr0 + (size_t)t * ldp + z_off + h * P + c_first + 4 * c);
+            sm4[(size_t)t * stride4 + 2 * N4 + c] = xv;
+            sm4[(size_t)t * stride4 + 2 * N4 + c4 + c] = zv;
+        }
+        for (int t = threadIdx.x; t < nt; t += blockDim.x) {  // the rows' step sizes and decays
+            const float dt = softplus_f(pr0[(size_t)t * ldp + dt_off + h] + bias);
+            sm[(size_t)t * stride + 2 * N + 2 * cols] = dt;
+            sm[(size_t)t * stride + 2 * N + 2 * cols + 1] = expf(a * dt);
+        }
+        __syncthreads();
+        for (int t = 0; t < nt; ++t) {
+            const float* tile = sm + (size_t)t * stride;
+            const float4* tile4 = reinterpret_cast<const float4*>(tile);
+            const float x = tile[2 * N + cl], decay = tile[2 * N + 2 * cols + 1];
+            const float dx = tile[2 * N + 2 * cols] * x;
+            float y = 0.0f, y1 = 0.0f;
+#pragma unroll
+            for (int m = 0; m < NC; ++m) {
+                const int c = g + 8 * m;
+                if (c < N4) {
+                    const float4 b = tile4[c], cc = tile4[N4 + c];
+                    S[m][0] = fmaf(S[m][0], decay, b.x * dx);
+                    S[m][1] = fmaf(S[m][1], decay, b.y * dx);
+                    S[m][2] = fmaf(S[m][2], decay, b.z * dx);
+                    S[m][3] = fmaf(S[m][3], decay, b.w * dx);
+                    y = fmaf(S[m][0], cc.x, fmaf(S[m][1], cc.y, y));
+                    y1 = fmaf(S[m][2], cc.z, fmaf(S[m][3], cc.w, y1));
+                }
+            }
+            y += y1;
+            y += __shfl_xor_sync(0xffffffffu, y, 4);
+            y += __shfl_xor_sync(0xffffffffu, y, 8);
+            y += __shfl_xor_sync(0xffffffffu, y, 16);
+            if (g == 0) {
+                y = fmaf(dcoef, x, y);
+                const float z = tile[2 * N + cols + cl];
+                st<TO>(out, (size_t)(t0 + t) * inner + h * P + col, y * (z / (1.0f + expf(-z))));
+            }
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < NC; ++m)
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+            if (g + 8 * m < N4) Sg[4 * (g + 8 * m) + q] = S[m][q];
+}
+
+template <int NC, typename TO>
+int launch_warp(const float* xbc, int ldx, const float* proj, int ldp, int z_off, int dt_off, const float* dt_bias,
+                const float* A, const float* D, float* state, long long state_stride, long long state_off,
+                const int* seq_slot, const int* seq_row0, int n_seq, void* out, int heads, int P, int N, int groups,
+                cudaStream_t s) {
+    // channels a block owns (four a warp): the largest divisor of P that is a multiple of
+    // four and at most 64; fewer while the blocks do not fill the SMs
+    int cols = 0;
+    for (int c = 4; c <= 64 && c <= P; c += 4)
+        if (P % c == 0) cols = c;
+    if (!cols) return RFX_ERR_UNSUPPORTED;
+    while (cols % 8 == 0 && cols > 16 && (long long)n_seq * heads * (P / cols) < sm_count()) cols /= 2;
+    const int stride = 2 * N + 2 * cols + 4;
+    int TT = (48 * 1024) / (stride * (int)sizeof(float));
+    if (TT > 32) TT = 32;
+    if (TT < 1) TT = 1;
+    const size_t smem = (size_t)TT * stride * sizeof(float);
+    auto kernel = ssd_scan_warp_kernel<NC, TO>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    dim3 grid(n_seq, heads, P / cols);
+    RFX_LAUNCH(kernel, grid, (cols / 4) * 32, smem, s, xbc, ldx, proj, ldp, z_off, dt_off, dt_bias, A, D, state,
+               state_stride, state_off, seq_slot, seq_row0, (TO*)out, heads, P, N, groups, cols, TT);
+    return 0;
+}
+
 }  // namespace
 
 extern "C" int rfx_ssd_scan(const float* xbc, int ldx, const float* proj, int ldp, int z_off, int dt_off,
@@ -94,6 +220,19 @@ extern "C" int rfx_ssd_scan(const float* xbc, int ldx, const float* proj, int ld
                             int n_seq, void* out, int out_dt, int heads, int P, int N, int groups, void* stream) {
     if (n_seq <= 0) return 0;
     if (heads <= 0 || groups <= 0 || heads % groups || P <= 0 || N <= 0) return RFX_ERR_BAD_ARG;
+    const bool aligned = ((ldx | ldp | z_off) & 3) == 0 &&
+                         ((reinterpret_cast<uintptr_t>(xbc) | reinterpret_cast<uintptr_t>(proj)) & 15) == 0;
+    if (P % 4 == 0 && N % 4 == 0 && N <= 256 && out_dt == RFX_DT_F32 && aligned) {
+#define RFX_WARP(NP)                                                                                          \
+    return launch_warp<NP, float>(xbc, ldx, proj, ldp, z_off, dt_off, dt_bias, A, D, state, state_stride,     \
+                                  state_off, seq_slot, seq_row0, n_seq, out, heads, P, N, groups,             \
+                                  (cudaStream_t)stream)
+        if (N <= 32) RFX_WARP(1);
+        if (N <= 64) RFX_WARP(2);
+        if (N <= 128) RFX_WARP(4);
+        RFX_WARP(8);
+#undef RFX_WARP
+    }
     // the slice of channels a block owns, fixed by P alone: how a row's sums are ordered
     // does not depend on what else is in the step
     int PW = P;

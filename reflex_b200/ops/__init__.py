@@ -1391,6 +1391,25 @@ def xielu_(a: torch.Tensor, alpha_pos: float, alpha_neg: float) -> torch.Tensor:
     return a
 
 
+def linear_xielu(x: torch.Tensor, weight: torch.Tensor, alpha_pos: float, alpha_neg: float) -> torch.Tensor:
+    """xielu(x @ W.T), [R, I] in x's dtype.  For a few bfloat16 rows the activation is
+    the product kernel's epilogue (on the 32-bit sums, rounded once); otherwise product,
+    then the activation in place."""
+    R, K = x.shape
+    if (x.dtype == torch.bfloat16 and R <= GEMV_MAX_ROWS and K % 8 == 0 and FUSE_GLU
+            and (x.data_ptr() | weight.data_ptr()) % 16 == 0):
+        N = weight.shape[0]
+        _chk(x, "x", torch.bfloat16)
+        _chk(weight, "weight", torch.bfloat16)
+        y = _new((R, N), torch.bfloat16, x.device)
+        st = native.lib().rfx_gemm_bf16_tc_xielu(
+            x.data_ptr(), weight.data_ptr(), y.data_ptr(), BF16, R, N, K, 0, float(alpha_pos), float(alpha_neg),
+            device_error_word(x.device).data_ptr(), _stream())
+        native.check(st, f"gemm_bf16_tc_xielu (R={R}, N={N}, K={K})")
+        return y
+    return xielu_(linear(x, weight), alpha_pos, alpha_neg)
+
+
 def loop_input_(x: torch.Tensor, x0: Optional[torch.Tensor], vec: torch.Tensor) -> torch.Tensor:
     """x[r] += x0[r] (when given) + vec, float32: the start of a pass over a repeated stretch."""
     R, H = x.shape

@@ -33,6 +33,8 @@ _SIGNATURES = {
     "rfx_gemm_bf16_tc_glu_clamped": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
                                      c_float, c_void_p, c_void_p],
     "rfx_gemm_bf16_tc_relu2": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "rfx_gemm_bf16_tc_xielu": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_float,
+                               c_void_p, c_void_p],
     "rfx_gemm_bf16_tc_residual": [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
                                   c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "rfx_gemm_bf16_tc_qkv": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_float, c_void_p, c_void_p,

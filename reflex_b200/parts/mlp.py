@@ -150,7 +150,8 @@ class XieluFeedForward:
     """out = W_down act(W_up x) with act(z) = ap z^2 + z / 2 for z > 0 and
     an (e^z - 1 - z) + z / 2 otherwise, ap = softplus(p) and an = beta +
     softplus(q), p and q the two stored numbers of the layer (`act`), beta the
-    spec's parameter.  The two softplus are taken once, when the weights are bound."""
+    spec's parameter.  The two softplus are taken once, when the weights are bound.
+    For a few rows the activation is the product kernel's epilogue (`ops.linear_xielu`)."""
 
     capturable = True
 
@@ -180,7 +181,7 @@ class XieluFeedForward:
         self.alpha_pos, self.alpha_neg = softplus(p), self.beta + softplus(q)
 
     def forward(self, x, residual=None):
-        act = ops.xielu_(ops.linear(x, self.up), self.alpha_pos, self.alpha_neg)
+        act = ops.linear_xielu(x, self.up, self.alpha_pos, self.alpha_neg)
         ops.prof_mark("ffn_gate_up")
         out = ops.linear(act, self.down, out_dtype=torch.float32)
         ops.prof_mark("ffn_down")
