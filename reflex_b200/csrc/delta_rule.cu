@@ -111,12 +111,13 @@ delta_rule_kernel(const float* __restrict__ proj, int ld, int r_off, int k_off, 
 // tiles of TT: all its threads first stage a tile (k, a, w, r and v of its rows into
 // shared memory, 16 bytes a load, then a warp a row: the unit key's norm by the lanes'
 // butterfly, u and a * u), then each warp walks the tile's rows on its own four
-// columns with no further barrier: lane (g, c) holds the key channels 4 (g + 8 m) ..
-// + 3 of column c in registers (NC groups of four, read from the tile 16 bytes at a
-// time), the eight partial sums of u^T S and of S^T r meet by shuffles.  The state
+// columns (four, two or one) with no further barrier: KG lanes (8, 16 or 32) share a
+// column, lane (g, c) holds its key channels 4 (g + KG m) .. + 3 in registers (NC groups
+// of four, read from the tile 16 bytes at a time), the KG partial sums of u^T S and of
+// S^T r meet by shuffles.  The state
 // lies [heads][value column][key channel].  Which block and warp walks a column
 // changes nothing of its arithmetic.
-template <int NC, typename TO>
+template <int NC, int KG, typename TO>
 __global__ void __launch_bounds__(512)
 delta_rule_warp_kernel(const float* __restrict__ proj, int ld, int r_off, int k_off, int v_off, int a_off,
                        const float* __restrict__ wpre, const float* __restrict__ w_bias,
@@ -127,7 +128,8 @@ delta_rule_warp_kernel(const float* __restrict__ proj, int ld, int r_off, int k_
     pdl_prologue();
     const int seq = blockIdx.x, h = blockIdx.y, c_first = blockIdx.z * cols;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-    const int g = lane >> 2, col = c_first + warp * 4 + (lane & 3);
+    constexpr int CW = 32 / KG;  // columns a warp walks; KG lanes share a column
+    const int g = lane / CW, col = c_first + warp * CW + (lane % CW);
     const int row0 = seq_row0[seq], row1 = seq_row0[seq + 1];
     const int hd = heads * d, d4 = d / 4;
     float* Sg = state + (size_t)seq_slot[seq] * state_stride + state_off + ((size_t)h * d + col) * d;
@@ -135,7 +137,7 @@ delta_rule_warp_kernel(const float* __restrict__ proj, int ld, int r_off, int k_
 #pragma unroll
     for (int m = 0; m < NC; ++m)
 #pragma unroll
-        for (int q = 0; q < 4; ++q) S[m][q] = g + 8 * m < d4 ? Sg[4 * (g + 8 * m) + q] : 0.0f;
+        for (int q = 0; q < 4; ++q) S[m][q] = g + KG * m < d4 ? Sg[4 * (g + KG * m) + q] : 0.0f;
     const float4* ab4 = reinterpret_cast<const float4*>(a_bias + h * d);
     const float4* wb4 = reinterpret_cast<const float4*>(w_bias + h * d);
     for (int t0 = row0; t0 < row1; t0 += TT) {
@@ -181,7 +183,7 @@ delta_rule_warp_kernel(const float* __restrict__ proj, int ld, int r_off, int k_
             float acc = 0.0f, acc1 = 0.0f;
 #pragma unroll
             for (int m = 0; m < NC; ++m) {
-                const int c = g + 8 * m;
+                const int c = g + KG * m;
                 if (c < d4) {
                     const float4 u = tile[d4 + c];
                     acc = fmaf(u.x, S[m][0], fmaf(u.y, S[m][1], acc));
@@ -189,14 +191,13 @@ delta_rule_warp_kernel(const float* __restrict__ proj, int ld, int r_off, int k_
                 }
             }
             acc += acc1;
-            acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 8);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 16);
+#pragma unroll
+            for (int off = CW; off < 32; off <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
             const float vj = reinterpret_cast<const float*>(tile)[5 * d + col];
             float o = 0.0f, o1 = 0.0f;
 #pragma unroll
             for (int m = 0; m < NC; ++m) {
-                const int c = g + 8 * m;
+                const int c = g + KG * m;
                 if (c < d4) {
                     const float4 k = tile[c], au = tile[2 * d4 + c], w = tile[3 * d4 + c], r = tile[4 * d4 + c];
                     S[m][0] = fmaf(k.x, vj, fmaf(w.x, S[m][0], -au.x * acc));
@@ -208,9 +209,8 @@ delta_rule_warp_kernel(const float* __restrict__ proj, int ld, int r_off, int k_
                 }
             }
             o += o1;
-            o += __shfl_xor_sync(0xffffffffu, o, 4);
-            o += __shfl_xor_sync(0xffffffffu, o, 8);
-            o += __shfl_xor_sync(0xffffffffu, o, 16);
+#pragma unroll
+            for (int off = CW; off < 32; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
             if (g == 0) st<TO>(out, (size_t)(t0 + t) * hd + h * d + col, o);
         }
     }
@@ -218,29 +218,31 @@ delta_rule_warp_kernel(const float* __restrict__ proj, int ld, int r_off, int k_
     for (int m = 0; m < NC; ++m)
 #pragma unroll
         for (int q = 0; q < 4; ++q)
-            if (g + 8 * m < d4) Sg[4 * (g + 8 * m) + q] = S[m][q];
+            if (g + KG * m < d4) Sg[4 * (g + KG * m) + q] = S[m][q];
 }
 
-template <int NC, typename TO>
+template <int NC, int KG, typename TO>
 int launch_warp(const float* proj, int ld, int r_off, int k_off, int v_off, int a_off, const float* wpre,
                 const float* w_bias, const float* a_bias, float rate, float unit_eps, float* state,
                 long long state_stride, long long state_off, const int* seq_slot, const int* seq_row0, int n_seq,
                 void* out, int heads, int d, cudaStream_t s) {
     // value columns a block owns (four a warp): fewer while the blocks do not fill the SMs
-    int cols = d <= 64 ? d : 64;
-    if (d % cols) return RFX_ERR_UNSUPPORTED;
-    while (cols % 8 == 0 && cols > 16 && (long long)n_seq * heads * (d / cols) < sm_count()) cols /= 2;
+    constexpr int CW = 32 / KG;  // columns a warp
+    int cols = d;
+    while (cols > 16 * CW && cols % (2 * CW) == 0) cols /= 2;  // at most 16 warps a block
+    if (cols > 16 * CW || d % cols) return RFX_ERR_UNSUPPORTED;
+    while (cols % (2 * CW) == 0 && cols > 4 * CW && (long long)n_seq * heads * (d / cols) < sm_count()) cols /= 2;
     int TT = (48 * 1024) / (6 * d * (int)sizeof(float));
     if (TT > 32) TT = 32;
     if (TT < 1) TT = 1;
     const size_t smem = (size_t)TT * 6 * d * sizeof(float);
-    auto kernel = delta_rule_warp_kernel<NC, TO>;
+    auto kernel = delta_rule_warp_kernel<NC, KG, TO>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
     dim3 grid(n_seq, heads, d / cols);
-    RFX_LAUNCH(kernel, grid, (cols / 4) * 32, smem, s, proj, ld, r_off, k_off, v_off, a_off, wpre, w_bias, a_bias,
+    RFX_LAUNCH(kernel, grid, (cols / CW) * 32, smem, s, proj, ld, r_off, k_off, v_off, a_off, wpre, w_bias, a_bias,
                rate, unit_eps, state, state_stride, state_off, seq_slot, seq_row0, (TO*)out, heads, d, cols, TT);
     return 0;
 }
@@ -258,14 +260,18 @@ extern "C" int rfx_delta_rule(const float* proj, int ld, int r_off, int k_off, i
                          ((reinterpret_cast<uintptr_t>(proj) | reinterpret_cast<uintptr_t>(wpre) |
                            reinterpret_cast<uintptr_t>(w_bias) | reinterpret_cast<uintptr_t>(a_bias)) & 15) == 0;
     if (d % 4 == 0 && d <= 256 && out_dt == RFX_DT_F32 && aligned) {
-#define RFX_WARP(N)                                                                                          \
-    return launch_warp<N, float>(proj, ld, r_off, k_off, v_off, a_off, wpre, w_bias, a_bias, rate, unit_eps, \
-                                 state, state_stride, state_off, seq_slot, seq_row0, n_seq, out, heads, d,   \
-                                 (cudaStream_t)stream)
-        if (d <= 32) RFX_WARP(1);
-        if (d <= 64) RFX_WARP(2);
-        if (d <= 128) RFX_WARP(4);
-        RFX_WARP(8);
+#define RFX_WARP(N, G)                                                                                          \
+    return launch_warp<N, G, float>(proj, ld, r_off, k_off, v_off, a_off, wpre, w_bias, a_bias, rate, unit_eps, \
+                                    state, state_stride, state_off, seq_slot, seq_row0, n_seq, out, heads, d,   \
+                                    (cudaStream_t)stream)
+        // as many lanes a column as it has groups of four key channels (8, 16 or 32): a lane's share
+        // is one or two groups, and a head gives enough warps to keep the SMs' schedulers busy
+        // (measured at 2,048 rows of 32 heads of 64: 1.0 ms with eight lanes a column and two groups
+        // a lane, 2.0 ms with two lanes and eight groups)
+        if (d <= 32) RFX_WARP(1, 8);
+        if (d <= 64) RFX_WARP(1, 16);
+        if (d <= 128) RFX_WARP(1, 32);
+        RFX_WARP(2, 32);
 #undef RFX_WARP
     }
     // the slice of value channels a block owns, fixed by d alone

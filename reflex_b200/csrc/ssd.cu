@@ -93,12 +93,13 @@ ssd_scan_kernel(const float* __restrict__ xbc, int ldx, const float* __restrict_
 // A block owns (sequence, head, some of the channels) and walks the rows in tiles of
 // TT: all its threads first stage a tile (B, C, x and z of its rows, 16 bytes a load,
 // their step sizes and decays into shared memory), then each warp walks the tile's
-// rows on its own four channels with no further barrier: lane (g, c) holds the states
-// 4 (g + 8 m) .. + 3 of channel c in registers (NC groups of four, B and C read from
-// the tile 16 bytes at a time), the eight partial sums of y meet by shuffles.  The
+// rows on its own channels (four, two or one) with no further barrier: KG lanes (8, 16 or
+// 32) share a channel, lane (g, c) holds its states 4 (g + KG m) .. + 3 in registers (NC
+// groups of four, B and C read from the tile 16 bytes at a time), the KG partial sums of y
+// meet by shuffles.  The
 // state lies [heads][channel][state].  Which block and warp walks a channel changes
 // nothing of its arithmetic.
-template <int NC, typename TO>
+template <int NC, int KG, typename TO>
 __global__ void __launch_bounds__(512)
 ssd_scan_warp_kernel(const float* __restrict__ xbc, int ldx, const float* __restrict__ proj, int ldp, int z_off,
                      int dt_off, const float* __restrict__ dt_bias, const float* __restrict__ A,
@@ -109,7 +110,8 @@ ssd_scan_warp_kernel(const float* __restrict__ xbc, int ldx, const float* __rest
     pdl_prologue();
     const int seq = blockIdx.x, h = blockIdx.y, c_first = blockIdx.z * cols;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int g = lane >> 2, cl = warp * 4 + (lane & 3), col = c_first + cl;
+    constexpr int CW = 32 / KG;  // channels a warp walks; KG lanes share a channel
+    const int g = lane / CW, cl = warp * CW + (lane % CW), col = c_first + cl;
     const int grp = h / (heads / groups);
     const int inner = heads * P, N4 = N / 4, c4 = cols / 4;
     const int row0 = seq_row0[seq], row1 = seq_row0[seq + 1];
@@ -119,7 +121,7 @@ ssd_scan_warp_kernel(const float* __restrict__ xbc, int ldx, const float* __rest
 #pragma unroll
     for (int m = 0; m < NC; ++m)
 #pragma unroll
-        for (int q = 0; q < 4; ++q) S[m][q] = g + 8 * m < N4 ? Sg[4 * (g + 8 * m) + q] : 0.0f;
+        for (int q = 0; q < 4; ++q) S[m][q] = g + KG * m < N4 ? Sg[4 * (g + KG * m) + q] : 0.0f;
     const float a = A[h], dcoef = D ? D[h] : 0.0f, bias = dt_bias ? dt_bias[h] : 0.0f;
     float4* sm4 = reinterpret_cast<float4*>(sm);
     for (int t0 = row0; t0 < row1; t0 += TT) {
@@ -155,7 +157,7 @@ ssd_scan_warp_kernel(const float* __restrict__ xbc, int ldx, const float* __rest
             float y = 0.0f, y1 = 0.0f;
 #pragma unroll
             for (int m = 0; m < NC; ++m) {
-                const int c = g + 8 * m;
+                const int c = g + KG * m;
                 if (c < N4) {
                     const float4 b = tile4[c], cc = tile4[N4 + c];
                     S[m][0] = fmaf(S[m][0], decay, b.x * dx);
@@ -167,9 +169,8 @@ ssd_scan_warp_kernel(const float* __restrict__ xbc, int ldx, const float* __rest
                 }
             }
             y += y1;
-            y += __shfl_xor_sync(0xffffffffu, y, 4);
-            y += __shfl_xor_sync(0xffffffffu, y, 8);
-            y += __shfl_xor_sync(0xffffffffu, y, 16);
+#pragma unroll
+            for (int off = CW; off < 32; off <<= 1) y += __shfl_xor_sync(0xffffffffu, y, off);
             if (g == 0) {
                 y = fmaf(dcoef, x, y);
                 const float z = tile[2 * N + cols + cl];
@@ -181,33 +182,35 @@ ssd_scan_warp_kernel(const float* __restrict__ xbc, int ldx, const float* __rest
     for (int m = 0; m < NC; ++m)
 #pragma unroll
         for (int q = 0; q < 4; ++q)
-            if (g + 8 * m < N4) Sg[4 * (g + 8 * m) + q] = S[m][q];
+            if (g + KG * m < N4) Sg[4 * (g + KG * m) + q] = S[m][q];
 }
 
-template <int NC, typename TO>
+template <int NC, int KG, typename TO>
 int launch_warp(const float* xbc, int ldx, const float* proj, int ldp, int z_off, int dt_off, const float* dt_bias,
                 const float* A, const float* D, float* state, long long state_stride, long long state_off,
                 const int* seq_slot, const int* seq_row0, int n_seq, void* out, int heads, int P, int N, int groups,
                 cudaStream_t s) {
     // channels a block owns (four a warp): the largest divisor of P that is a multiple of
     // four and at most 64; fewer while the blocks do not fill the SMs
+    constexpr int CW = 32 / KG;  // channels a warp
+    // (a multiple of four: x and z are staged 16 bytes a load)
     int cols = 0;
-    for (int c = 4; c <= 64 && c <= P; c += 4)
+    for (int c = 4; c <= 16 * CW && c <= P; c += 4)
         if (P % c == 0) cols = c;
     if (!cols) return RFX_ERR_UNSUPPORTED;
-    while (cols % 8 == 0 && cols > 16 && (long long)n_seq * heads * (P / cols) < sm_count()) cols /= 2;
+    while (cols % 8 == 0 && cols > 4 * CW && cols > 4 && (long long)n_seq * heads * (P / cols) < sm_count()) cols /= 2;
     const int stride = 2 * N + 2 * cols + 4;
     int TT = (48 * 1024) / (stride * (int)sizeof(float));
     if (TT > 32) TT = 32;
     if (TT < 1) TT = 1;
     const size_t smem = (size_t)TT * stride * sizeof(float);
-    auto kernel = ssd_scan_warp_kernel<NC, TO>;
+    auto kernel = ssd_scan_warp_kernel<NC, KG, TO>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
     dim3 grid(n_seq, heads, P / cols);
-    RFX_LAUNCH(kernel, grid, (cols / 4) * 32, smem, s, xbc, ldx, proj, ldp, z_off, dt_off, dt_bias, A, D, state,
+    RFX_LAUNCH(kernel, grid, (cols / CW) * 32, smem, s, xbc, ldx, proj, ldp, z_off, dt_off, dt_bias, A, D, state,
                state_stride, state_off, seq_slot, seq_row0, (TO*)out, heads, P, N, groups, cols, TT);
     return 0;
 }
@@ -223,14 +226,17 @@ extern "C" int rfx_ssd_scan(const float* xbc, int ldx, const float* proj, int ld
     const bool aligned = ((ldx | ldp | z_off) & 3) == 0 &&
                          ((reinterpret_cast<uintptr_t>(xbc) | reinterpret_cast<uintptr_t>(proj)) & 15) == 0;
     if (P % 4 == 0 && N % 4 == 0 && N <= 256 && out_dt == RFX_DT_F32 && aligned) {
-#define RFX_WARP(NP)                                                                                          \
-    return launch_warp<NP, float>(xbc, ldx, proj, ldp, z_off, dt_off, dt_bias, A, D, state, state_stride,     \
-                                  state_off, seq_slot, seq_row0, n_seq, out, heads, P, N, groups,             \
-                                  (cudaStream_t)stream)
-        if (N <= 32) RFX_WARP(1);
-        if (N <= 64) RFX_WARP(2);
-        if (N <= 128) RFX_WARP(4);
-        RFX_WARP(8);
+#define RFX_WARP(NP, G)                                                                                       \
+    return launch_warp<NP, G, float>(xbc, ldx, proj, ldp, z_off, dt_off, dt_bias, A, D, state, state_stride,  \
+                                     state_off, seq_slot, seq_row0, n_seq, out, heads, P, N, groups,          \
+                                     (cudaStream_t)stream)
+        // as many lanes a channel as it has groups of four states (8, 16 or 32): a lane's share is one
+        // or two groups, and a head gives enough warps to keep the SMs' schedulers busy
+        if (N <= 32) RFX_WARP(1, 8);
+        if (N <= 64 && P % 2 == 0) RFX_WARP(1, 16);
+        if (N <= 64) RFX_WARP(2, 8);
+        if (N <= 128) RFX_WARP(1, 32);
+        RFX_WARP(2, 32);
 #undef RFX_WARP
     }
     // the slice of channels a block owns, fixed by P alone: how a row's sums are ordered

@@ -70,6 +70,22 @@ def test_xielu_pass_start_tanh_columns_and_scaled_sum(dtype):
     assert relerr(ops().scaled_sum_(a.clone().to(DEV), b.to(DEV), 0.6, -1.5), (0.6 * a - 1.5 * b).double().numpy()) < 1e-6
 
 
+@pytest.mark.parametrize("R,N,K", [(1, 96, 64), (8, 1000, 328), (33, 256, 2048), (64, 152, 72), (65, 64, 64), (3, 77, 64),
+                                   (5, 250, 200)])
+def test_xielu_as_the_products_epilogue(R, N, K):
+    """A few bfloat16 rows: the activation rides in the product kernel (on the 32-bit
+    sums); more rows, or a width that is no multiple of 8: product, then the kernel."""
+    g = torch.Generator().manual_seed(R + N)
+    x = (torch.randn(R, K, generator=g)).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * 0.2).to(torch.bfloat16)
+    ap, an = float(pz.softplus(0.4)), 0.5 + float(pz.softplus(-0.3))
+    ref = pz.xielu(x.double().numpy() @ w.double().numpy().T, 0.4, -0.3)
+    out = ops().linear_xielu(x.to(DEV), w.to(DEV), ap, an)
+    assert out.dtype == torch.bfloat16 and relerr(out, ref) < 1.2e-2
+    x32, w32 = x.float(), w.float()
+    assert relerr(ops().linear_xielu(x32.to(DEV), w32.to(DEV), ap, an), ref) < 1e-5
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("nq,nkv,d,dv,rot,col0,extra", [
     (4, 2, 16, 24, (100.0, 8), 0, 64), (3, 3, 40, 16, (1000.0, 20), 8, 120), (8, 2, 128, 64, (500000.0, 32), 0, 0),
