@@ -25,6 +25,18 @@ namespace {
 
 using namespace rfx;
 
+// fewest warps a block of the warp-walking form keeps when its columns are cut further to fill
+// the SMs (REFLEX_B200_SCAN_MIN_WARPS, a tuning aid read once)
+inline int scan_min_warps() {
+    static int v = 0;
+    if (!v) {
+        const char* e = getenv("REFLEX_B200_SCAN_MIN_WARPS");
+        v = e ? atoi(e) : 16;
+        if (v < 1 || v > 16) v = 16;
+    }
+    return v;
+}
+
 __device__ __forceinline__ float sigmoid_f(float t) { return 1.0f / (1.0f + expf(-t)); }
 
 template <typename TO>
@@ -178,40 +190,55 @@ delta_rule_warp_kernel(const float* __restrict__ proj, int ld, int r_off, int k_
             }
         }
         __syncthreads();
-        for (int t = 0; t < nt; ++t) {
-            const float4* tile = reinterpret_cast<const float4*>(sm + (size_t)t * 6 * d);
-            float acc = 0.0f, acc1 = 0.0f;
+        // four rows at a time: u^T S must meet before the state's step (one chain of shuffles a
+        // row), the rows' partial sums of S^T r meet together afterwards (their chains side by side)
+        for (int t = 0; t < nt; t += 4) {
+            float ov[4];
 #pragma unroll
-            for (int m = 0; m < NC; ++m) {
-                const int c = g + KG * m;
-                if (c < d4) {
-                    const float4 u = tile[d4 + c];
-                    acc = fmaf(u.x, S[m][0], fmaf(u.y, S[m][1], acc));
-                    acc1 = fmaf(u.z, S[m][2], fmaf(u.w, S[m][3], acc1));
+            for (int u4 = 0; u4 < 4; ++u4) {
+                ov[u4] = 0.0f;
+                if (t + u4 < nt) {
+                    const float4* tile = reinterpret_cast<const float4*>(sm + (size_t)(t + u4) * 6 * d);
+                    float acc = 0.0f, acc1 = 0.0f;
+#pragma unroll
+                    for (int m = 0; m < NC; ++m) {
+                        const int c = g + KG * m;
+                        if (c < d4) {
+                            const float4 u = tile[d4 + c];
+                            acc = fmaf(u.x, S[m][0], fmaf(u.y, S[m][1], acc));
+                            acc1 = fmaf(u.z, S[m][2], fmaf(u.w, S[m][3], acc1));
+                        }
+                    }
+                    acc += acc1;
+#pragma unroll
+                    for (int off = CW; off < 32; off <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+                    const float vj = reinterpret_cast<const float*>(tile)[5 * d + col];
+                    float o = 0.0f, o1 = 0.0f;
+#pragma unroll
+                    for (int m = 0; m < NC; ++m) {
+                        const int c = g + KG * m;
+                        if (c < d4) {
+                            const float4 k = tile[c], au = tile[2 * d4 + c], w = tile[3 * d4 + c], r = tile[4 * d4 + c];
+                            S[m][0] = fmaf(k.x, vj, fmaf(w.x, S[m][0], -au.x * acc));
+                            S[m][1] = fmaf(k.y, vj, fmaf(w.y, S[m][1], -au.y * acc));
+                            S[m][2] = fmaf(k.z, vj, fmaf(w.z, S[m][2], -au.z * acc));
+                            S[m][3] = fmaf(k.w, vj, fmaf(w.w, S[m][3], -au.w * acc));
+                            o = fmaf(S[m][0], r.x, fmaf(S[m][1], r.y, o));
+                            o1 = fmaf(S[m][2], r.z, fmaf(S[m][3], r.w, o1));
+                        }
+                    }
+                    ov[u4] = o + o1;
                 }
             }
-            acc += acc1;
 #pragma unroll
-            for (int off = CW; off < 32; off <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-            const float vj = reinterpret_cast<const float*>(tile)[5 * d + col];
-            float o = 0.0f, o1 = 0.0f;
+            for (int off = CW; off < 32; off <<= 1)
 #pragma unroll
-            for (int m = 0; m < NC; ++m) {
-                const int c = g + KG * m;
-                if (c < d4) {
-                    const float4 k = tile[c], au = tile[2 * d4 + c], w = tile[3 * d4 + c], r = tile[4 * d4 + c];
-                    S[m][0] = fmaf(k.x, vj, fmaf(w.x, S[m][0], -au.x * acc));
-                    S[m][1] = fmaf(k.y, vj, fmaf(w.y, S[m][1], -au.y * acc));
-                    S[m][2] = fmaf(k.z, vj, fmaf(w.z, S[m][2], -au.z * acc));
-                    S[m][3] = fmaf(k.w, vj, fmaf(w.w, S[m][3], -au.w * acc));
-                    o = fmaf(S[m][0], r.x, fmaf(S[m][1], r.y, o));
-                    o1 = fmaf(S[m][2], r.z, fmaf(S[m][3], r.w, o1));
-                }
+                for (int u4 = 0; u4 < 4; ++u4) ov[u4] += __shfl_xor_sync(0xffffffffu, ov[u4], off);
+            if (g == 0) {
+#pragma unroll
+                for (int u4 = 0; u4 < 4; ++u4)
+                    if (t + u4 < nt) st<TO>(out, (size_t)(t0 + t + u4) * hd + h * d + col, ov[u4]);
             }
-            o += o1;
-#pragma unroll
-            for (int off = CW; off < 32; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
-            if (g == 0) st<TO>(out, (size_t)(t0 + t) * hd + h * d + col, o);
         }
     }
 #pragma unroll
@@ -231,7 +258,8 @@ int launch_warp(const float* proj, int ld, int r_off, int k_off, int v_off, int 
     int cols = d;
     while (cols > 16 * CW && cols % (2 * CW) == 0) cols /= 2;  // at most 16 warps a block
     if (cols > 16 * CW || d % cols) return RFX_ERR_UNSUPPORTED;
-    while (cols % (2 * CW) == 0 && cols > 4 * CW && (long long)n_seq * heads * (d / cols) < sm_count()) cols /= 2;
+    while (cols % (2 * CW) == 0 && cols > scan_min_warps() * CW && (long long)n_seq * heads * (d / cols) < sm_count())
+        cols /= 2;
     int TT = (48 * 1024) / (6 * d * (int)sizeof(float));
     if (TT > 32) TT = 32;
     if (TT < 1) TT = 1;

@@ -26,6 +26,18 @@ namespace {
 
 using namespace rfx;
 
+// fewest warps a block of the warp-walking form keeps when its columns are cut further to fill
+// the SMs (REFLEX_B200_SCAN_MIN_WARPS, a tuning aid read once)
+inline int scan_min_warps() {
+    static int v = 0;
+    if (!v) {
+        const char* e = getenv("REFLEX_B200_SCAN_MIN_WARPS");
+        v = e ? atoi(e) : 16;
+        if (v < 1 || v > 16) v = 16;
+    }
+    return v;
+}
+
 __device__ __forceinline__ float softplus_f(float v) { return fmaxf(v, 0.0f) + log1pf(expf(-fabsf(v))); }
 
 template <typename TO>
@@ -106,7 +118,7 @@ ssd_scan_warp_kernel(const float* __restrict__ xbc, int ldx, const float* __rest
                      const float* __restrict__ D, float* __restrict__ state, long long state_stride,
                      long long state_off, const int* __restrict__ seq_slot, const int* __restrict__ seq_row0,
                      TO* __restrict__ out, int heads, int P, int N, int groups, int cols, int TT) {
-    extern __shared__ __align__(16) float sm[];  // [TT][2 N + 2 cols + 4]: B, C, x, z, dt, decay
+    extern __shared__ __align__(16) float sm[];  // [TT][2 N + 2 cols + 4]: B, C, x, silu(z), dt, decay
     pdl_prologue();
     const int seq = blockIdx.x, h = blockIdx.y, c_first = blockIdx.z * cols;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -141,7 +153,10 @@ ssd_scan_warp_kernel(const float* __restrict__ xbc, int ldx, const float* __rest
             const float4 xv = *reinterpret_cast<const float4*>(xr0 + (size_t)t * ldx + h * P + c_first + 4 * c);
             const float4 zv = *reinterpret_cast<const float4*>(pr0 + (size_t)t * ldp + z_off + h * P + c_first + 4 * c);
             sm4[(size_t)t * stride4 + 2 * N4 + c] = xv;
-            sm4[(size_t)t * stride4 + 2 * N4 + c4 + c] = zv;
+            // the gate silu(z), made once an element here
+            sm4[(size_t)t * stride4 + 2 * N4 + c4 + c] =
+                make_float4(zv.x / (1.0f + expf(-zv.x)), zv.y / (1.0f + expf(-zv.y)), zv.z / (1.0f + expf(-zv.z)),
+                            zv.w / (1.0f + expf(-zv.w)));
         }
         for (int t = threadIdx.x; t < nt; t += blockDim.x) {  // the rows' step sizes and decays
             const float dt = softplus_f(pr0[(size_t)t * ldp + dt_off + h] + bias);
@@ -149,32 +164,48 @@ ssd_scan_warp_kernel(const float* __restrict__ xbc, int ldx, const float* __rest
             sm[(size_t)t * stride + 2 * N + 2 * cols + 1] = expf(a * dt);
         }
         __syncthreads();
-        for (int t = 0; t < nt; ++t) {
-            const float* tile = sm + (size_t)t * stride;
-            const float4* tile4 = reinterpret_cast<const float4*>(tile);
-            const float x = tile[2 * N + cl], decay = tile[2 * N + 2 * cols + 1];
-            const float dx = tile[2 * N + 2 * cols] * x;
-            float y = 0.0f, y1 = 0.0f;
+        // four rows at a time: the state's steps follow one another, the rows' partial sums of y
+        // meet by shuffles together (their chains run side by side), then the rows are written
+        for (int t = 0; t < nt; t += 4) {
+            float yv[4], xs[4];
 #pragma unroll
-            for (int m = 0; m < NC; ++m) {
-                const int c = g + KG * m;
-                if (c < N4) {
-                    const float4 b = tile4[c], cc = tile4[N4 + c];
-                    S[m][0] = fmaf(S[m][0], decay, b.x * dx);
-                    S[m][1] = fmaf(S[m][1], decay, b.y * dx);
-                    S[m][2] = fmaf(S[m][2], decay, b.z * dx);
-                    S[m][3] = fmaf(S[m][3], decay, b.w * dx);
-                    y = fmaf(S[m][0], cc.x, fmaf(S[m][1], cc.y, y));
-                    y1 = fmaf(S[m][2], cc.z, fmaf(S[m][3], cc.w, y1));
+            for (int u = 0; u < 4; ++u) {
+                yv[u] = 0.0f;
+                xs[u] = 0.0f;
+                if (t + u < nt) {
+                    const float* tile = sm + (size_t)(t + u) * stride;
+                    const float4* tile4 = reinterpret_cast<const float4*>(tile);
+                    const float x = tile[2 * N + cl], decay = tile[2 * N + 2 * cols + 1];
+                    const float dx = tile[2 * N + 2 * cols] * x;
+                    float y = 0.0f, y1 = 0.0f;
+#pragma unroll
+                    for (int m = 0; m < NC; ++m) {
+                        const int c = g + KG * m;
+                        if (c < N4) {
+                            const float4 b = tile4[c], cc = tile4[N4 + c];
+                            S[m][0] = fmaf(S[m][0], decay, b.x * dx);
+                            S[m][1] = fmaf(S[m][1], decay, b.y * dx);
+                            S[m][2] = fmaf(S[m][2], decay, b.z * dx);
+                            S[m][3] = fmaf(S[m][3], decay, b.w * dx);
+                            y = fmaf(S[m][0], cc.x, fmaf(S[m][1], cc.y, y));
+                            y1 = fmaf(S[m][2], cc.z, fmaf(S[m][3], cc.w, y1));
+                        }
+                    }
+                    yv[u] = y + y1;
+                    xs[u] = x;
                 }
             }
-            y += y1;
 #pragma unroll
-            for (int off = CW; off < 32; off <<= 1) y += __shfl_xor_sync(0xffffffffu, y, off);
+            for (int off = CW; off < 32; off <<= 1)
+#pragma unroll
+                for (int u = 0; u < 4; ++u) yv[u] += __shfl_xor_sync(0xffffffffu, yv[u], off);
             if (g == 0) {
-                y = fmaf(dcoef, x, y);
-                const float z = tile[2 * N + cols + cl];
-                st<TO>(out, (size_t)(t0 + t) * inner + h * P + col, y * (z / (1.0f + expf(-z))));
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    if (t + u < nt) {
+                        const float gate = sm[(size_t)(t + u) * stride + 2 * N + cols + cl];  // silu(z)
+                        st<TO>(out, (size_t)(t0 + t + u) * inner + h * P + col, fmaf(dcoef, xs[u], yv[u]) * gate);
+                    }
             }
         }
     }
@@ -198,7 +229,8 @@ int launch_warp(const float* xbc, int ldx, const float* proj, int ldp, int z_off
     for (int c = 4; c <= 16 * CW && c <= P; c += 4)
         if (P % c == 0) cols = c;
     if (!cols) return RFX_ERR_UNSUPPORTED;
-    while (cols % 8 == 0 && cols > 4 * CW && cols > 4 && (long long)n_seq * heads * (P / cols) < sm_count()) cols /= 2;
+    while (cols % 8 == 0 && cols > scan_min_warps() * CW && cols > 4 && (long long)n_seq * heads * (P / cols) < sm_count())
+        cols /= 2;
     const int stride = 2 * N + 2 * cols + 4;
     int TT = (48 * 1024) / (stride * (int)sizeof(float));
     if (TT > 32) TT = 32;
