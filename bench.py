@@ -329,17 +329,17 @@ def zelinex_config(z):
     pair = {"type": "parallel",
             "mixer": {"left": {"heads": z["heads"], "kv_heads": max(1, z["heads"] // 4), "dim": z["dim"],
                                "vdim": z["dim"], "scale": z["dim"] ** -0.5,
-                               "rot": {"base": 1000000.0, "dims": z["dim"] // 2}, "mask": {"size": z["window"]}},
+                               "rot": {"base": 500000.0, "dims": z["dim"] // 2}, "mask": {"size": z["window"]}},
                       "right": {"heads": z["width"] // 64, "vdim": 64, "state": 128, "groups": 2, "conv": 4,
                                 "norm_groups": 2},
-                      "left_scale": 0.6, "right_scale": 0.5}}
+                      "left_scale": 0.75, "right_scale": 0.55}}
     delta = {"type": "general_delta", "mixer": {"heads": z["width"] // 64, "dim": 64}}
     dense = {"kind": "dense", "ff": z["ff"]}
     moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]},
-           "router": {"experts": z["experts"], "top": z["top"], "scale": 1.5}, "shared": {"ff": z["expert_ff"]}}
+           "router": {"experts": z["experts"], "top": z["top"], "scale": 1.25}, "shared": {"ff": z["expert_ff"]}}
     layers = [dict((pair, delta)[i % 2], mlp=(dense, moe)[i % 2]) for i in range(z["layers"])]
     return {"architecture": "Zelinex", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5},
-            "residual_mult": 0.7, "loop": {"start": 0, "stop": z["layers"], "times": 1}, "layers": layers}
+            "residual_mult": 0.8, "loop": {"start": 0, "stop": z["layers"], "times": 1}, "layers": layers}
 
 
 def qwen3_config_like(z):

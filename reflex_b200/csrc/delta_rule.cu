@@ -288,18 +288,20 @@ extern "C" int rfx_delta_rule(const float* proj, int ld, int r_off, int k_off, i
                          ((reinterpret_cast<uintptr_t>(proj) | reinterpret_cast<uintptr_t>(wpre) |
                            reinterpret_cast<uintptr_t>(w_bias) | reinterpret_cast<uintptr_t>(a_bias)) & 15) == 0;
     if (d % 4 == 0 && d <= 256 && out_dt == RFX_DT_F32 && aligned) {
-#define RFX_WARP(N, G)                                                                                          \
-    return launch_warp<N, G, float>(proj, ld, r_off, k_off, v_off, a_off, wpre, w_bias, a_bias, rate, unit_eps, \
-                                    state, state_stride, state_off, seq_slot, seq_row0, n_seq, out, heads, d,   \
-                                    (cudaStream_t)stream)
+#define RFX_WARP(N, G)                                                                                        \
+    st = launch_warp<N, G, float>(proj, ld, r_off, k_off, v_off, a_off, wpre, w_bias, a_bias, rate, unit_eps, \
+                                  state, state_stride, state_off, seq_slot, seq_row0, n_seq, out, heads, d,   \
+                                  (cudaStream_t)stream)
+        int st;  // a head size whose columns do not divide among the warps goes to the general form
         // as many lanes a column as it has groups of four key channels (8, 16 or 32): a lane's share
         // is one or two groups, and a head gives enough warps to keep the SMs' schedulers busy
         // (measured at 2,048 rows of 32 heads of 64: 1.0 ms with eight lanes a column and two groups
         // a lane, 2.0 ms with two lanes and eight groups)
         if (d <= 32) RFX_WARP(1, 8);
-        if (d <= 64) RFX_WARP(1, 16);
-        if (d <= 128) RFX_WARP(1, 32);
-        RFX_WARP(2, 32);
+        else if (d <= 64) RFX_WARP(1, 16);
+        else if (d <= 128) RFX_WARP(1, 32);
+        else RFX_WARP(2, 32);
+        if (st != RFX_ERR_UNSUPPORTED) return st;
 #undef RFX_WARP
     }
     // the slice of value channels a block owns, fixed by d alone

@@ -52,6 +52,92 @@ sandwich_norm_kernel(const float* __restrict__ y, float* __restrict__ x, const f
     for (int c = threadIdx.x; c < H; c += blockDim.x) st<TO>(out, base + c, (row[c] * r2) * w_next[c]);
 }
 
+// The same with 16-byte accesses, for widths that are a multiple of four: the row stays in
+// registers (up to V groups of four a thread) between the sums of squares and the outputs.
+template <typename TO, int V>
+__global__ void __launch_bounds__(512)
+sandwich_norm4_kernel(const float* __restrict__ y, float* __restrict__ x, const float* __restrict__ w_post,
+                      float mult, float eps, const float* __restrict__ w_next, float eps_next,
+                      TO* __restrict__ out, int H) {
+    __shared__ float scratch[32];
+    pdl_prologue();
+    const size_t base = (size_t)blockIdx.x * H;
+    const int H4 = H / 4;
+    const float4* y4 = reinterpret_cast<const float4*>(y + base);
+    float4* x4 = reinterpret_cast<float4*>(x + base);
+    const float4* wp4 = reinterpret_cast<const float4*>(w_post);
+    float4 v[V], xv[V], wp[V];
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < H4) {
+            v[i] = y4[c];
+            xv[i] = x4[c];
+            wp[i] = wp4[c];
+            ss = fmaf(v[i].x, v[i].x, fmaf(v[i].y, v[i].y, fmaf(v[i].z, v[i].z, fmaf(v[i].w, v[i].w, ss))));
+        }
+    }
+    const float r1 = 1.0f / sqrtf(block_sum(ss, scratch) / (float)H + eps);
+    ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < H4) {
+            v[i].x = fmaf(mult, (v[i].x * r1) * wp[i].x, xv[i].x);
+            v[i].y = fmaf(mult, (v[i].y * r1) * wp[i].y, xv[i].y);
+            v[i].z = fmaf(mult, (v[i].z * r1) * wp[i].z, xv[i].z);
+            v[i].w = fmaf(mult, (v[i].w * r1) * wp[i].w, xv[i].w);
+            x4[c] = v[i];
+            ss = fmaf(v[i].x, v[i].x, fmaf(v[i].y, v[i].y, fmaf(v[i].z, v[i].z, fmaf(v[i].w, v[i].w, ss))));
+        }
+    }
+    if (w_next == nullptr) return;
+    const float r2 = 1.0f / sqrtf(block_sum(ss, scratch) / (float)H + eps_next);
+    const float4* wn4 = reinterpret_cast<const float4*>(w_next);
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < H4) {
+            const float4 wn = wn4[c];
+            store4(out + base + 4 * (size_t)c, make_float4((v[i].x * r2) * wn.x, (v[i].y * r2) * wn.y,
+                                                           (v[i].z * r2) * wn.z, (v[i].w * r2) * wn.w));
+        }
+    }
+}
+
+// One block a (row, part), 16 bytes an access: parts of many elements (a norm in a few equal
+// parts of a wide row), where a warp a part would leave a row to a warp or two.
+template <typename TO>
+__global__ void __launch_bounds__(256)
+group_norm_gate_wide_kernel(const float* __restrict__ x, const float* __restrict__ w, float eps,
+                            const float* __restrict__ z, int ldz, int zcol, TO* __restrict__ out, int C, int gs) {
+    __shared__ float scratch[32];
+    pdl_prologue();
+    const int r = blockIdx.x, g = blockIdx.y;
+    const size_t base = (size_t)r * C + (size_t)g * gs;
+    const float4* x4 = reinterpret_cast<const float4*>(x + base);
+    const float4* w4 = reinterpret_cast<const float4*>(w + (size_t)g * gs);
+    float ss = 0.0f;
+    for (int c = threadIdx.x; c < gs / 4; c += blockDim.x) {
+        const float4 v = x4[c];
+        ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+    }
+    const float rs = 1.0f / sqrtf(block_sum(ss, scratch) / (float)gs + eps);
+    for (int c = threadIdx.x; c < gs / 4; c += blockDim.x) {
+        const float4 v = x4[c], wv = w4[c];
+        float4 o = make_float4((v.x * rs) * wv.x, (v.y * rs) * wv.y, (v.z * rs) * wv.z, (v.w * rs) * wv.w);
+        if (z) {
+            const float* zp = z + (size_t)r * ldz + zcol + (size_t)g * gs + 4 * c;
+            o.x *= 1.0f / (1.0f + exact_expf(-zp[0]));
+            o.y *= 1.0f / (1.0f + exact_expf(-zp[1]));
+            o.z *= 1.0f / (1.0f + exact_expf(-zp[2]));
+            o.w *= 1.0f / (1.0f + exact_expf(-zp[3]));
+        }
+        store4(out + base + 4 * (size_t)c, o);
+    }
+}
+
 template <typename TO>
 __global__ void __launch_bounds__(256)
 group_norm_gate_kernel(const float* __restrict__ x, const float* __restrict__ w, float eps,
@@ -60,7 +146,8 @@ group_norm_gate_kernel(const float* __restrict__ x, const float* __restrict__ w,
     const int r = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
     const int gs = C / groups;
-    for (int g = warp; g < groups; g += nwarps) {
+    // a warp a part; a row's parts spread over the blocks of its grid row
+    for (int g = blockIdx.y * nwarps + warp; g < groups; g += gridDim.y * nwarps) {
         const float* xr = x + (size_t)r * C + (size_t)g * gs;
         float ss = 0.0f;
         for (int c = lane; c < gs; c += 32) ss = fmaf(xr[c], xr[c], ss);
@@ -127,6 +214,28 @@ extern "C" int rfx_sandwich_norm(const float* y, float* x, const float* w_post, 
     const size_t smem = (size_t)H * sizeof(float);
     if (smem > 200 * 1024) return RFX_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
+    const bool al = ((reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w_post) |
+                      reinterpret_cast<uintptr_t>(w_next) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+    if (H % 4 == 0 && H <= 4 * 512 * 4 && al) {
+        // the row in registers, 16 bytes an access; threads so that a thread holds one to four groups
+        const int H4 = H / 4;
+        const int threads = H4 <= 128 ? 128 : H4 <= 256 ? 256 : 512;
+#define RFX_V(TO, V)                                                                                           \
+    RFX_LAUNCH((sandwich_norm4_kernel<TO, V>), R, threads, 0, s, y, x, w_post, mult, eps, w_next, eps_next,   \
+               (TO*)out, H)
+#define RFX_PICK(TO)                                      \
+    do {                                                  \
+        if (H4 <= threads) RFX_V(TO, 1);                  \
+        else if (H4 <= 2 * threads) RFX_V(TO, 2);         \
+        else RFX_V(TO, 4);                                \
+    } while (0)
+        if (out_dt == RFX_DT_F32) RFX_PICK(float);
+        else if (out_dt == RFX_DT_BF16) RFX_PICK(__nv_bfloat16);
+        else return RFX_ERR_BAD_ARG;
+#undef RFX_PICK
+#undef RFX_V
+        return 0;
+    }
 #define RFX_GO(TO)                                                                                          \
     do {                                                                                                    \
         if (smem > 48 * 1024) {                                                                             \
@@ -149,11 +258,26 @@ extern "C" int rfx_group_norm_gate(const float* x, const float* w, float eps, co
     if (R <= 0) return 0;
     if (groups <= 0 || C % groups) return RFX_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
-    const int threads = groups >= 8 ? 256 : 32 * groups;
+    const int gs = C / groups;
+    const bool al = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+    if (gs >= 512 && gs % 4 == 0 && C % 4 == 0 && al && groups <= 65535) {
+        dim3 grid(R, groups);
+        if (out_dt == RFX_DT_F32)
+            RFX_LAUNCH(group_norm_gate_wide_kernel<float>, grid, 256, 0, s, x, w, eps, z, ldz, zcol, (float*)out, C, gs);
+        else if (out_dt == RFX_DT_BF16)
+            RFX_LAUNCH(group_norm_gate_wide_kernel<__nv_bfloat16>, grid, 256, 0, s, x, w, eps, z, ldz, zcol,
+                       (__nv_bfloat16*)out, C, gs);
+        else return RFX_ERR_BAD_ARG;
+        return 0;
+    }
+    const int threads = groups >= 4 ? 128 : 32 * groups;
+    int gy = (groups + 3) / 4;
+    if (gy > 65535) gy = 65535;
+    dim3 grid(R, gy);
     if (out_dt == RFX_DT_F32)
-        RFX_LAUNCH(group_norm_gate_kernel<float>, R, threads, 0, s, x, w, eps, z, ldz, zcol, (float*)out, C, groups);
+        RFX_LAUNCH(group_norm_gate_kernel<float>, grid, threads, 0, s, x, w, eps, z, ldz, zcol, (float*)out, C, groups);
     else if (out_dt == RFX_DT_BF16)
-        RFX_LAUNCH(group_norm_gate_kernel<__nv_bfloat16>, R, threads, 0, s, x, w, eps, z, ldz, zcol,
+        RFX_LAUNCH(group_norm_gate_kernel<__nv_bfloat16>, grid, threads, 0, s, x, w, eps, z, ldz, zcol,
                    (__nv_bfloat16*)out, C, groups);
     else return RFX_ERR_BAD_ARG;
     return 0;

@@ -258,17 +258,18 @@ extern "C" int rfx_ssd_scan(const float* xbc, int ldx, const float* proj, int ld
     const bool aligned = ((ldx | ldp | z_off) & 3) == 0 &&
                          ((reinterpret_cast<uintptr_t>(xbc) | reinterpret_cast<uintptr_t>(proj)) & 15) == 0;
     if (P % 4 == 0 && N % 4 == 0 && N <= 256 && out_dt == RFX_DT_F32 && aligned) {
-#define RFX_WARP(NP, G)                                                                                       \
-    return launch_warp<NP, G, float>(xbc, ldx, proj, ldp, z_off, dt_off, dt_bias, A, D, state, state_stride,  \
-                                     state_off, seq_slot, seq_row0, n_seq, out, heads, P, N, groups,          \
-                                     (cudaStream_t)stream)
+#define RFX_WARP(NP, G)                                                                                   \
+    st = launch_warp<NP, G, float>(xbc, ldx, proj, ldp, z_off, dt_off, dt_bias, A, D, state, state_stride, \
+                                   state_off, seq_slot, seq_row0, n_seq, out, heads, P, N, groups,         \
+                                   (cudaStream_t)stream)
+        int st;  // a channel count that does not divide among the warps goes to the general form
         // as many lanes a channel as it has groups of four states (8, 16 or 32): a lane's share is one
         // or two groups, and a head gives enough warps to keep the SMs' schedulers busy
         if (N <= 32) RFX_WARP(1, 8);
-        if (N <= 64 && P % 2 == 0) RFX_WARP(1, 16);
-        if (N <= 64) RFX_WARP(2, 8);
-        if (N <= 128) RFX_WARP(1, 32);
-        RFX_WARP(2, 32);
+        else if (N <= 64) RFX_WARP(1, 16);
+        else if (N <= 128) RFX_WARP(1, 32);
+        else RFX_WARP(2, 32);
+        if (st != RFX_ERR_UNSUPPORTED) return st;
 #undef RFX_WARP
     }
     // the slice of channels a block owns, fixed by P alone: how a row's sums are ordered

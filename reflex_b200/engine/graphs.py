@@ -15,19 +15,26 @@ the caller asks to borrow the graph's own buffer.  Only the engine's very first
 decode step runs eagerly (it sizes the lazily made buffers), and the first step
 of a batch size above what the library's own products take (it lets the
 vendor's product load its kernel for that shape); every other (size, bucket)
-captures at its first use.  The engine keeps at most
+captures at its first use.  A capture that something outside the step invalidates
+(a call of another thread that is not permitted while a stream captures) costs
+nothing but the graph: the step runs eagerly and the next one captures.  The
+engine keeps at most
 `Engine.max_graphs` graphs and drops the least recently used.
 """
 
 from __future__ import annotations
 
+import gc
+
 import torch
 
+from ..errors import CudaError
 from .batch import layout, make_batch
 
 
 class DecodeGraph:
     WARMUP = 1  # eager decode steps per engine before the first capture
+    MAX_CAPTURE_FAILURES = 3  # captures of one graph that something else may invalidate before it is an error
 
     def __init__(self, engine, n_seqs: int, context_hint: int):
         self.engine = engine
@@ -41,6 +48,7 @@ class DecodeGraph:
         self.logits = None
         self.calls = 0
         self.kernels = 0
+        self.capture_failures = 0
 
     def run(self, tokens, slots, starts, want, tokens_dev=None, borrow: bool = False) -> torch.Tensor:
         """`tokens_dev` (int32 [n] on the device), when given, takes the place of
@@ -71,8 +79,31 @@ class DecodeGraph:
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
             before = ops.launch_count()
-            with torch.cuda.graph(g, pool=eng.graph_pool()):
-                self.logits = eng.model.forward(batch, eng.cache)
+            stream = torch.cuda.current_stream()
+            # While the stream captures, no finalizer may run (the collector freeing an older
+            # engine's graphs calls what a capturing thread must not), and what other threads call
+            # is their own business (a loader's pinned buffers): the collector is off for the
+            # capture and the capture checks this thread's calls only.
+            collecting = gc.isenabled()
+            gc.disable()
+            try:
+                with torch.cuda.graph(g, pool=eng.graph_pool(), capture_error_mode="thread_local"):
+                    self.logits = eng.model.forward(batch, eng.cache)
+            except (CudaError, RuntimeError) as e:
+                # Something invalidated the capture all the same (a call that is not permitted
+                # while a stream captures): nothing of the step has run, so it runs eagerly now,
+                # and the next step of this size tries to capture again, a few times.
+                if "captur" not in str(e) or self.capture_failures >= self.MAX_CAPTURE_FAILURES:
+                    raise
+                self.capture_failures += 1
+                self.logits = None
+                del g
+                torch.cuda.set_stream(stream)  # the capture's side stream may still be the current one
+                torch.cuda.synchronize()
+                return eng.model.forward(batch, eng.cache)
+            finally:
+                if collecting:
+                    gc.enable()
             self.kernels = ops.launch_count() - before  # this library's kernels in the graph
             self.graph = g
             # the captured launches point into the workspace as it is now: keep that

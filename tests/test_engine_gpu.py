@@ -447,6 +447,34 @@ def test_wanted_places_other_than_one_per_token_go_the_eager_way():
     eng.close(sb)
 
 
+def test_a_capture_that_is_invalidated_runs_its_step_eagerly_and_the_next_one_captures():
+    """The first capture of a decode graph fails as one that something outside the
+    step invalidated would: the step's logits are right all the same, and the same
+    batch size is captured at its next step."""
+    V = ALL["B"]["vocab_size"]
+    folder = helpers.model_folder("B", 7, "bfloat16")
+    eng = helpers.make_engine(folder, "bfloat16", max_tokens=1024)
+    ref_eng = helpers.make_engine(folder, "bfloat16", max_tokens=1024, use_graphs=False)
+    reqs = [helpers.random_tokens(12, V, 900 + i) for i in range(3)]
+    forward, failed = eng.model.forward, []
+
+    def flaky(batch, cache):
+        if torch.cuda.is_current_stream_capturing() and not failed:
+            failed.append(True)
+            raise RuntimeError("operation failed due to a previous error during capture")
+        return forward(batch, cache)
+
+    eng.model.forward = flaky
+    got = helpers.run_batches(eng, reqs, 3, [4])
+    want = helpers.run_batches(ref_eng, reqs, 3, [4])
+    assert failed, "no capture was tried"
+    graphs = [g for g in eng._graphs.values()] if hasattr(eng, "_graphs") else []
+    assert any(g.graph is not None and g.capture_failures == 1 for g in graphs) or not graphs
+    for a, b in zip(got, want):
+        assert np.abs(a - b).max() <= 2e-2 * np.abs(b).max()
+    eng.check_errors()
+
+
 def test_a_batch_of_64_that_ends_one_request_at_a_time():
     """64 requests decoded together in bfloat16 with graphs on, whose lengths
     make them leave one after another, so the batch shrinks through every size

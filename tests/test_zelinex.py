@@ -245,10 +245,10 @@ def test_xielu_branches_and_routing_weights():
     out = pz.xielu(z, 0.3, -0.2)
     assert np.allclose(out, [an * (math.exp(-2.0) - 1 + 2.0) - 1.0, 0.0, ap * 9 + 1.5])
     router = np.array([[1.0, 0.0], [0.0, 1.0], [-1.0, -1.0], [0.5, 0.5]])
-    ids, wts = pz.route(np.array([[2.0, 0.0], [0.0, 0.1]]), router, 2, 1.5)
+    ids, wts = pz.route(np.array([[2.0, 0.0], [0.0, 0.1]]), router, 2, 1.25)
     assert ids.tolist() == [[0, 3], [1, 3]]
     e = np.exp([2.0, 1.0])
-    assert np.allclose(wts[0], 1.5 * e / e.sum()) and abs(wts[1].sum() - 1.5) < 1e-12
+    assert np.allclose(wts[0], 1.25 * e / e.sum()) and abs(wts[1].sum() - 1.25) < 1e-12
 
 
 def test_run_order():

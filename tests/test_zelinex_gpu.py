@@ -31,13 +31,13 @@ def test_norm_after_a_sublayer_and_before_the_next_in_one_pass(R, H, out_dtype):
     g = torch.Generator().manual_seed(R + H)
     x, y = torch.randn(R, H, generator=g) * 2, torch.randn(R, H, generator=g) * 5
     wp, wn = torch.rand(H, generator=g) + 0.5, torch.rand(H, generator=g) + 0.5
-    new = x.double().numpy() + 0.7 * pz.rms_norm(y.double().numpy(), wp.double().numpy(), 1e-5)
+    new = x.double().numpy() + 0.65 * pz.rms_norm(y.double().numpy(), wp.double().numpy(), 1e-5)
     xd = x.to(DEV)
-    out = ops().sandwich_norm(y.to(DEV), xd, wp.to(DEV), 0.7, 1e-5, wn.to(DEV), 1e-6, out_dtype)
+    out = ops().sandwich_norm(y.to(DEV), xd, wp.to(DEV), 0.65, 1e-5, wn.to(DEV), 1e-6, out_dtype)
     assert relerr(xd, new) < 3e-6
     assert relerr(out, pz.rms_norm(new, wn.double().numpy(), 1e-6)) < tol(out_dtype)
     xd = x.to(DEV)
-    assert ops().sandwich_norm(y.to(DEV), xd, wp.to(DEV), 0.7, 1e-5, None, 0.0, out_dtype) is None
+    assert ops().sandwich_norm(y.to(DEV), xd, wp.to(DEV), 0.65, 1e-5, None, 0.0, out_dtype) is None
     assert relerr(xd, new) < 3e-6
 
 
@@ -67,7 +67,7 @@ def test_xielu_pass_start_tanh_columns_and_scaled_sum(dtype):
     rows = torch.randn(6, 50, generator=g) * 2
     assert relerr(ops().tanh_cols(rows.to(DEV), 13, 7, dtype), np.tanh(rows.double().numpy()[:, 13:20])) < tol(dtype, 2e-6)
     a, b = torch.randn(9, 41, generator=g), torch.randn(9, 41, generator=g)
-    assert relerr(ops().scaled_sum_(a.clone().to(DEV), b.to(DEV), 0.6, -1.5), (0.6 * a - 1.5 * b).double().numpy()) < 1e-6
+    assert relerr(ops().scaled_sum_(a.clone().to(DEV), b.to(DEV), 0.55, -1.5), (0.55 * a - 1.5 * b).double().numpy()) < 1e-6
 
 
 @pytest.mark.parametrize("R,N,K", [(1, 96, 64), (8, 1000, 328), (33, 256, 2048), (64, 152, 72), (65, 64, 64), (3, 77, 64),
@@ -171,7 +171,7 @@ def _sigmoid_ref(q, ks, vs, seqs, scale, window, bias, dtype):
 SIG_CASES = [  # nq, nkv, d, dv, [(start, n_new)], window
     (4, 2, 16, 24, [(0, 70), (130, 3), (0, 1)], 20),
     (2, 1, 64, 32, [(0, 200), (63, 2), (133, 3)], 70),
-    (6, 1, 64, 128, [(0, 300), (328, 4)], 136),
+    (6, 2, 64, 128, [(0, 300), (328, 4)], 150),
     (8, 2, 128, 64, [(0, 150), (200, 40)], 33),
     (3, 3, 40, 16, [(0, 140)], 64),                   # a window of exactly a page
     (12, 3, 32, 128, [(0, 260), (5, 1)], None),       # every earlier key
@@ -400,7 +400,7 @@ def test_a_slow_decay_keeps_a_far_input_and_a_removal_rate_of_one_forgets_it():
 
 @pytest.mark.parametrize("R", [1, 2, 5, 9, 70, 200])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("E,top,scale,shared", [(8, 3, 1.5, 64), (4, 2, 1.0, 0), (1, 1, 2.0, 16), (3, 3, 0.5, 0)])
+@pytest.mark.parametrize("E,top,scale,shared", [(8, 3, 1.25, 64), (4, 2, 1.0, 0), (1, 1, 2.0, 16), (3, 3, 0.5, 0)])
 def test_experts_with_scores_over_all_of_them_and_a_shared_expert(R, dtype, E, top, scale, shared):
     from reflex_b200.config.spec import FeedForwardSpec
     from reflex_b200.parts.moe import MixtureOfExperts
@@ -437,10 +437,10 @@ def test_experts_with_scores_over_all_of_them_and_a_shared_expert(R, dtype, E, t
 
 def test_routing_weights_and_ties():
     logits = torch.tensor([[0.0, 2.0, 2.0, -1.0, 1.0], [5.0, 5.0, 5.0, 5.0, 5.0], [-30.0, 40.0, 0.0, 39.0, 1.0]])
-    ids, wts = ops().moe_route(logits.to(DEV), None, 3, scores="softmax_all", scale=1.5)
+    ids, wts = ops().moe_route(logits.to(DEV), None, 3, scores="softmax_all", scale=1.25)
     assert ids.cpu().tolist() == [[1, 2, 4], [0, 1, 2], [1, 3, 4]]   # ties: the lower index
-    _ids, ref = pz.route(logits.double().numpy(), np.eye(5), 3, 1.5)
-    assert relerr(wts, ref) < 1e-6 and abs(float(wts[1].sum()) - 1.5) < 1e-6
+    _ids, ref = pz.route(logits.double().numpy(), np.eye(5), 3, 1.25)
+    assert relerr(wts, ref) < 1e-6 and abs(float(wts[1].sum()) - 1.25) < 1e-6
 
 
 # ----------------------------------------------------------------- whole models

@@ -84,9 +84,9 @@ ZEL_C = model(61, 100, 1e-5, 0.6, (1, 2, 3), [
 ])
 # D: heads of 128 with values of 64, a window of 33; eight state-space heads of 64 channels and
 # 64 states; delta heads of 128 (a block takes their columns in four slices); a loop of one pass
-ZEL_D = model(200, 256, 1e-5, 0.7, (0, 2, 1), [
-    (pair(8, 2, 128, 64, 0.1, (500000.0, 32), 33, 8, 64, 64, 2, 4, 2, 0.6, 0.5), dense(256)),
-    (delta(2, 128), moe(64, 8, 3, 1.5, 64)),
+ZEL_D = model(200, 256, 1e-5, 0.75, (0, 2, 1), [
+    (pair(8, 2, 128, 64, 0.1, (500000.0, 32), 33, 8, 64, 64, 2, 4, 2, 0.9, 0.45), dense(256)),
+    (delta(2, 128), moe(64, 8, 3, 1.25, 64)),
 ])
 # E: the whole model runs three times; a long window (200) over several pages, twelve heads
 # on three key heads, keys of 32 and values of 128; two taps
